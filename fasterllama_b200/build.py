@@ -1,0 +1,85 @@
+"""In-tree build of the native pieces: the CUDA attention library (sm_100a only) and, for the
+tests, the host oracle.  Run as `python -m fasterllama_b200.build` or through
+`__graft_entry__.build()`.  Nothing here needs a GPU: nvcc cross-compiles."""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(PKG_DIR)
+CSRC = os.path.join(PKG_DIR, "csrc")
+LIB_PATH = os.path.join(PKG_DIR, "libflb_attn.so")
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_LIB = os.path.join(ORACLE_DIR, "libflb_oracle.so")
+
+CUDA_SOURCES = ["decode_attn.cu", "prefill_attn.cu", "launch.cu"]
+NVCC_FLAGS = [
+    "-std=c++17", "-O3", "-lineinfo",
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared",
+]
+
+
+def _nvcc() -> str:
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found; the attention library cannot be built")
+    return cand
+
+
+def _newer(target: str, sources: list[str]) -> bool:
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= t for s in sources)
+
+
+def build_cuda(force: bool = False, verbose: bool = False) -> str:
+    srcs = [os.path.join(CSRC, s) for s in CUDA_SOURCES]
+    deps = srcs + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    deps.append(os.path.join(ROOT, "include", "flb_attn.h"))
+    if not force and _newer(LIB_PATH, deps):
+        return LIB_PATH
+    cmd = [_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", LIB_PATH, *srcs]
+    subprocess.run(cmd, check=True)
+    return LIB_PATH
+
+
+def build_oracle(force: bool = False) -> str:
+    src = os.path.join(ORACLE_DIR, "attn_oracle.cpp")
+    if not force and _newer(ORACLE_LIB, [src, os.path.join(ROOT, "include", "flb_attn.h")]):
+        return ORACLE_LIB
+    cmd = ["g++", "-O2", "-std=c++17", "-fopenmp", "-shared", "-fPIC", src, "-o", ORACLE_LIB]
+    subprocess.run(cmd, check=True)
+    return ORACLE_LIB
+
+
+def build_reference(force: bool = False) -> str | None:
+    """Compiles the reference's own CUDA kernels (from the read-only reference checkout, where
+    present) plus the runner in oracle/ref_runner.cu into oracle/_ref/.  Returns None when the
+    reference sources are not on this machine."""
+    script = os.path.join(ORACLE_DIR, "build_ref.sh")
+    if not os.path.exists(script):
+        return None
+    out = os.path.join(ORACLE_DIR, "_ref", "libflb_ref.so")
+    ref_root = os.environ.get("FLB_REFERENCE_ROOT", "/root/reference")
+    if not os.path.isdir(ref_root):
+        return out if os.path.exists(out) else None
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= os.path.getmtime(os.path.join(ORACLE_DIR, "ref_runner.cu")):
+        return out
+    subprocess.run(["bash", script, ref_root], check=True)
+    return out
+
+
+def build_all(force: bool = False, verbose: bool = False) -> None:
+    build_cuda(force, verbose)
+    build_oracle(force)
+    build_reference(force)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print("built", LIB_PATH)

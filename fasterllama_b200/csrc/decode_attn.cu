@@ -1,0 +1,414 @@
+// decode_attn.cu — masked multi-head decode attention over the KV cache, one launch.
+//
+// Replaces, for seq_len == 1, the reference's chain
+//   warpQKRoteEmbeddingTransposeKernel   fasterLlama/cuda/decoder_kernels.cu:425-464
+//   warpDequantizedVTransposeKernel      fasterLlama/cuda/decoder_kernels.cu:858-884
+//   storeKVcacheKernel                   fasterLlama/cuda/decoder_kernels.cu:597-611
+//   cublasSgemvStridedBatched (K.q)      fasterLlama/cuda/open_decoder.cu:194-201
+//   blockSoftmaxKernel                   fasterLlama/cuda/decoder_kernels.cu:800-835
+//   cublasSgemvStridedBatched (P.V)      fasterLlama/cuda/open_decoder.cu:231-238
+//
+// Shape of the kernel (HBM-bound: 1 FMA per 2 cache bytes, so CUDA cores suffice):
+//   * grid = (b,h) units x nsplit_max split-KV partitions of `split_len` cache rows; a CTA whose
+//     partition lies beyond its sequence's length leaves at once.
+//   * one producer warp streams the partition's K rows and V rows (each contiguous in the
+//     [B,H,T,d] cache) into a STAGES-deep shared-memory ring with 1-D bulk copies (TMA engine)
+//     that complete on mbarriers; NWARPS compute warps consume the ring.
+//   * a cache row is d*sizeof(CacheT) bytes = LPR lanes x 16 B; a warp takes 32/LPR rows per
+//     step, 16-byte shared loads, fp32 dot product, xor-shuffle reduction, and keeps its own
+//     online-softmax state (running max in the log2 domain, sum, d-wide accumulator striped
+//     over lanes).  Warps merge through shared memory in warp order.
+//   * the new token: every CTA rotates q (RoPE) itself; the CTA that owns the last partition
+//     also dequantises/rotates k, rounds k,v to the cache type, appends them at row `past` and
+//     folds the new key/value into its partial result from registers, so no CTA ever reads a
+//     row that another CTA writes in the same launch.
+//   * split merge: partial (max, sum, acc[d]) go to scratch; the CTA that arrives last for a
+//     (b,h) (one atomic counter, nobody waits) combines the partitions in partition order, so the
+//     result is a function of (sequence length, split_len) only.
+#include "decode_attn.cuh"
+#include "flb_ptx.cuh"
+
+namespace flb {
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+// blockSoftmaxKernel starts its running max at -1e9f (decoder_kernels.cu:811); same value in the
+// log2 domain.  It keeps fully-masked rows finite: every exp underflows to 0 and the sum is 0.
+constexpr float kMaxInit = -1e9f * kLog2e;
+
+template <typename T> struct CacheIO;
+template <> struct CacheIO<float> {
+    static __device__ __forceinline__ float round(float x) { return x; }
+    static __device__ __forceinline__ void store(float *p, float x) { *p = x; }
+    // 16 bytes = 4 floats
+    static __device__ __forceinline__ void unpack(const uint4 &u, float (&f)[4]) {
+        f[0] = __uint_as_float(u.x);
+        f[1] = __uint_as_float(u.y);
+        f[2] = __uint_as_float(u.z);
+        f[3] = __uint_as_float(u.w);
+    }
+};
+template <> struct CacheIO<__half> {
+    static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+    static __device__ __forceinline__ void store(__half *p, float x) { *p = __float2half_rn(x); }
+    // 16 bytes = 8 halves
+    static __device__ __forceinline__ void unpack(const uint4 &u, float (&f)[8]) {
+        const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 t = __half22float2(h[i]);
+            f[2 * i] = t.x;
+            f[2 * i + 1] = t.y;
+        }
+    }
+};
+
+// One element of q/k/v for (unit = b*H + h, dim i) with seq_len == 1: [B,1,H,d] -> unit*d + i.
+// FLB_IN_INT32: float(acc) * act_scale[b] * w_scale[h*d+i], in this order (decoder_kernels.cu:449).
+__device__ __forceinline__ float load_input(const DecodeArgs &a, const void *base, const float *w_scale, int unit, int b,
+                                            int h, int i) {
+    const size_t off = (size_t)unit * kHeadDim + i;
+    if (a.input_mode == 0) {
+        const float acc = (float)__ldg((const int32_t *)base + off);
+        return acc * __ldg(a.act_scale + b) * __ldg(w_scale + (size_t)h * kHeadDim + i);
+    } else if (a.input_mode == 1) {
+        return __ldg((const float *)base + off);
+    }
+    return __half2float(((const __half *)base)[off]);
+}
+
+} // namespace
+
+template <typename CacheT, int TILE_ROWS, int STAGES, int NWARPS>
+__global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(const __grid_constant__ DecodeArgs a) {
+    constexpr int D = kHeadDim;
+    constexpr int ROW_BYTES = D * (int)sizeof(CacheT);
+    constexpr int EPL = 16 / (int)sizeof(CacheT); // elements per lane (one 16-byte chunk)
+    constexpr int LPR = D / EPL;                  // lanes per cache row
+    constexpr int RPI = 32 / LPR;                 // rows a warp takes per step
+    constexpr int ITERS = TILE_ROWS / (NWARPS * RPI);
+    constexpr int TILE_BYTES = TILE_ROWS * ROW_BYTES;
+    constexpr int NC = NWARPS * 32; // compute threads
+    static_assert(ITERS * NWARPS * RPI == TILE_ROWS, "tile rows must divide over the compute warps");
+    static_assert(NC >= D, "need one compute thread per head dimension");
+    static_assert(LPR == 16 || LPR == 32, "row must span 16 or 32 lanes");
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + (size_t)STAGES * 2 * TILE_BYTES);
+    uint64_t *empty = full + STAGES;
+    float *q_s = reinterpret_cast<float *>(empty + STAGES); // [D] rotated q * scale * log2e
+    float *wm = q_s + D;                                    // [NWARPS]
+    float *wl = wm + NWARPS;                                // [NWARPS]
+    float *wo = wl + NWARPS;                                // [NWARPS][D]
+    float *red = wo + NWARPS * D;                           // [NWARPS]
+    int *flag = reinterpret_cast<int *>(red + NWARPS);
+
+    const int split = blockIdx.x % a.nsplit_max;
+    const int unit = blockIdx.x / a.nsplit_max; // b*H + h
+    const int b = unit / a.H, h = unit - b * a.H;
+    int past = a.past_lens ? __ldg(a.past_lens + b) : a.start_pos;
+    // a length outside [0, T-1] or beyond what the grid was sized for is flagged and clamped so
+    // that no access leaves the slab
+    const int past_cap = min(a.T - 1, a.nsplit_max * a.split_len);
+    if (past < 0 || past > past_cap) {
+        if (threadIdx.x == 0 && split == 0) atomicOr(a.status, 4u);
+        past = max(0, min(past, past_cap));
+    }
+    const int nsplit = max(1, (past + a.split_len - 1) / a.split_len);
+    if (split >= nsplit) return;
+
+    const int row0 = split * a.split_len;
+    const int rows = max(0, min(a.split_len, past - row0));
+    const int ntiles = (rows + TILE_ROWS - 1) / TILE_ROWS;
+    const bool is_last = (split == nsplit - 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], NWARPS);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    float vnew = 0.0f;   // thread t < D of the last partition: new v[t], rounded to the cache type
+    float s_new = 0.0f;  // score of the new key in the log2 domain
+    bool new_visible = false;
+
+    if (warp == NWARPS) {
+        // ---------------- producer warp: one lane issues the bulk copies -------------------
+        if (lane == 0) {
+            const unsigned char *kb = (const unsigned char *)a.k_cache + ((size_t)unit * a.T + row0) * ROW_BYTES;
+            const unsigned char *vb = (const unsigned char *)a.v_cache + ((size_t)unit * a.T + row0) * ROW_BYTES;
+            for (int t = 0; t < ntiles; ++t) {
+                const int s = t % STAGES;
+                const uint32_t use = (uint32_t)(t / STAGES);
+                if (!mbar_wait(&empty[s], (use & 1u) ^ 1u)) {
+                    atomicOr(a.status, kErrProducerWait);
+                    break;
+                }
+                const int r = min(TILE_ROWS, rows - t * TILE_ROWS);
+                const uint32_t bytes = (uint32_t)r * ROW_BYTES;
+                mbar_arrive_expect_tx(&full[s], 2u * bytes);
+                bulk_g2s(smem_raw + (size_t)s * 2 * TILE_BYTES, kb + (size_t)t * TILE_BYTES, bytes, &full[s]);
+                bulk_g2s(smem_raw + (size_t)s * 2 * TILE_BYTES + TILE_BYTES, vb + (size_t)t * TILE_BYTES, bytes, &full[s]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- compute warps ------------------------------------------------------
+        const int tid = threadIdx.x; // < NC
+        // -- the new token: dequantise, rotate, append (a2, a3, a4 of the reference in one place)
+        {
+            float qraw = 0.f, kraw = 0.f, vraw = 0.f;
+            if (tid < D) {
+                qraw = load_input(a, a.q, a.q_w_scale, unit, b, h, tid);
+                if (is_last) {
+                    kraw = load_input(a, a.k, a.k_w_scale, unit, b, h, tid);
+                    vraw = load_input(a, a.v, a.v_w_scale, unit, b, h, tid);
+                }
+            }
+            float qrot = qraw, krot = kraw;
+            if (a.freq_cis) {
+                // pairs (2i, 2i+1) sit in neighbouring lanes of one warp
+                const float qo = __shfl_xor_sync(0xffffffffu, qraw, 1);
+                const float ko = __shfl_xor_sync(0xffffffffu, kraw, 1);
+                if (tid < D) {
+                    const int row = a.rope_pos0 + (a.rope_add_past ? past : 0);
+                    const float *fr = a.freq_cis + (size_t)row * D;
+                    const float c = __ldg(fr + (tid & ~1)), sn = __ldg(fr + (tid | 1));
+                    if (tid & 1) {
+                        qrot = qraw * c + qo * sn;
+                        krot = kraw * c + ko * sn;
+                    } else {
+                        qrot = qraw * c - qo * sn;
+                        krot = kraw * c - ko * sn;
+                    }
+                }
+            }
+            float part = 0.f;
+            if (tid < D) {
+                const float qs = qrot * a.scale_log2e;
+                q_s[tid] = qs;
+                if (is_last) {
+                    const float kr = CacheIO<CacheT>::round(krot);
+                    vnew = CacheIO<CacheT>::round(vraw);
+                    const size_t c = ((size_t)unit * a.T + past) * D + tid;
+                    CacheIO<CacheT>::store((CacheT *)a.k_cache + c, krot);
+                    CacheIO<CacheT>::store((CacheT *)a.v_cache + c, vraw);
+                    part = qs * kr;
+                }
+            }
+            if (is_last) {
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+                if (lane == 0) red[warp] = part;
+            }
+            named_bar_sync(1, NC);
+            if (is_last) {
+                float t = 0.f;
+#pragma unroll
+                for (int w = 0; w < NWARPS; ++w) t += red[w];
+                s_new = t;
+                switch (a.mask_mode) {
+                case 1: // generic additive mask, row = query position, column = key position
+                    s_new += __ldg(a.attn_mask + (size_t)past * a.mask_row_stride + past) * kLog2e;
+                    new_visible = true;
+                    break;
+                case 3: // strictly causal: a token does not see itself
+                    new_visible = false;
+                    break;
+                default:
+                    new_visible = true;
+                    break;
+                }
+            }
+        }
+
+        const int c = lane % LPR;   // 16-byte chunk of the row this lane owns
+        const int sub = lane / LPR; // which of the RPI rows of a step
+        float qreg[EPL];
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) qreg[j] = q_s[c * EPL + j];
+
+        float m_run = kMaxInit, l_run = 0.f;
+        float o[EPL];
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) o[j] = 0.f;
+
+        const float *mask_row = (a.mask_mode == 1) ? a.attn_mask + (size_t)past * a.mask_row_stride + row0 : nullptr;
+
+        bool ok = true;
+        for (int t = 0; t < ntiles && ok; ++t) {
+            const int s = t % STAGES;
+            const uint32_t use = (uint32_t)(t / STAGES);
+            if (!mbar_wait(&full[s], use & 1u)) {
+                if (lane == 0) atomicOr(a.status, kErrConsumerWait);
+                ok = false;
+                break;
+            }
+            const CacheT *Kt = reinterpret_cast<const CacheT *>(smem_raw + (size_t)s * 2 * TILE_BYTES);
+            const CacheT *Vt = reinterpret_cast<const CacheT *>(smem_raw + (size_t)s * 2 * TILE_BYTES + TILE_BYTES);
+            const int rvalid = min(TILE_ROWS, rows - t * TILE_ROWS);
+
+            float sc[ITERS];
+#pragma unroll
+            for (int it = 0; it < ITERS; ++it) {
+                const int r = (it * NWARPS + warp) * RPI + sub;
+                const uint4 kv = *reinterpret_cast<const uint4 *>(Kt + (size_t)r * D + c * EPL);
+                float kf[EPL];
+                CacheIO<CacheT>::unpack(kv, kf);
+                float acc = 0.f;
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) acc = fmaf(qreg[j], kf[j], acc);
+                sc[it] = acc;
+            }
+#pragma unroll
+            for (int it = 0; it < ITERS; ++it) {
+#pragma unroll
+                for (int off = LPR / 2; off > 0; off >>= 1) sc[it] += __shfl_xor_sync(0xffffffffu, sc[it], off);
+            }
+            float mt = kMaxInit;
+#pragma unroll
+            for (int it = 0; it < ITERS; ++it) {
+                const int r = (it * NWARPS + warp) * RPI + sub;
+                if (r >= rvalid) {
+                    sc[it] = -INFINITY;
+                } else if (mask_row) {
+                    sc[it] += __ldg(mask_row + t * TILE_ROWS + r) * kLog2e;
+                }
+                mt = fmaxf(mt, sc[it]);
+            }
+            if (RPI == 2) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
+            const float m_new = fmaxf(m_run, mt);
+            const float corr = ex2(m_run - m_new);
+            m_run = m_new;
+            l_run *= corr;
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) o[j] *= corr;
+#pragma unroll
+            for (int it = 0; it < ITERS; ++it) {
+                const int r = (it * NWARPS + warp) * RPI + sub;
+                if (r < rvalid) {
+                    const float p = ex2(sc[it] - m_new);
+                    l_run += p;
+                    const uint4 vv = *reinterpret_cast<const uint4 *>(Vt + (size_t)r * D + c * EPL);
+                    float vf[EPL];
+                    CacheIO<CacheT>::unpack(vv, vf);
+#pragma unroll
+                    for (int j = 0; j < EPL; ++j) o[j] = fmaf(p, vf[j], o[j]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+
+        if (RPI == 2) {
+            l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) o[j] += __shfl_xor_sync(0xffffffffu, o[j], 16);
+        }
+        if (sub == 0) {
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) wo[warp * D + c * EPL + j] = o[j];
+        }
+        if (lane == 0) {
+            wm[warp] = m_run;
+            wl[warp] = l_run;
+        }
+    }
+    __syncthreads();
+
+    // ---------------- merge the compute warps (warp order), add the new token ----------------
+    const int tid = threadIdx.x;
+    float acc = 0.f, lsum = 0.f, M = kMaxInit;
+    if (tid < D) {
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, wm[w]);
+        if (is_last && new_visible) M = fmaxf(M, s_new);
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) {
+            const float e = ex2(wm[w] - M);
+            acc = fmaf(wo[w * D + tid], e, acc);
+            lsum = fmaf(wl[w], e, lsum);
+        }
+        if (is_last && new_visible) {
+            const float p = ex2(s_new - M);
+            acc = fmaf(p, vnew, acc);
+            lsum += p;
+        }
+    }
+
+    if (nsplit == 1) {
+        if (tid < D) {
+            const float r = (lsum > 0.f) ? acc / lsum : 0.f;
+            const size_t oo = (size_t)unit * D + tid;
+            if (a.out_f16)
+                ((__half *)a.out)[oo] = __float2half_rn(r);
+            else
+                ((float *)a.out)[oo] = r;
+        }
+        return;
+    }
+
+    // ---------------- split-KV: publish the partial, the last arriver merges ------------------
+    const size_t pbase = (size_t)unit * a.nsplit_max;
+    if (tid < D) {
+        a.part_o[(pbase + split) * D + tid] = acc;
+        if (tid == 0) {
+            a.part_ml[(pbase + split) * 2 + 0] = M;
+            a.part_ml[(pbase + split) * 2 + 1] = lsum;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned old = atomicAdd(a.counters + unit, 1u);
+        *flag = (old == (unsigned)(nsplit - 1));
+    }
+    __syncthreads();
+    if (!*flag) return;
+    __threadfence();
+    if (tid < D) {
+        float M2 = kMaxInit;
+        for (int i = 0; i < nsplit; ++i) M2 = fmaxf(M2, __ldcg(a.part_ml + (pbase + i) * 2));
+        float acc2 = 0.f, l2 = 0.f;
+        for (int i = 0; i < nsplit; ++i) {
+            const float e = ex2(__ldcg(a.part_ml + (pbase + i) * 2) - M2);
+            acc2 = fmaf(__ldcg(a.part_o + (pbase + i) * D + tid), e, acc2);
+            l2 = fmaf(__ldcg(a.part_ml + (pbase + i) * 2 + 1), e, l2);
+        }
+        const float r = (l2 > 0.f) ? acc2 / l2 : 0.f;
+        const size_t oo = (size_t)unit * D + tid;
+        if (a.out_f16)
+            ((__half *)a.out)[oo] = __float2half_rn(r);
+        else
+            ((float *)a.out)[oo] = r;
+        if (tid == 0) a.counters[unit] = 0u; // ready for the next call
+    }
+}
+
+// ---- host-side launcher ------------------------------------------------------------------
+
+template <typename CacheT, int TILE_ROWS, int STAGES, int NWARPS>
+static cudaError_t launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
+    constexpr int TILE_BYTES = TILE_ROWS * kHeadDim * (int)sizeof(CacheT);
+    constexpr size_t smem = (size_t)STAGES * 2 * TILE_BYTES + 2 * STAGES * sizeof(uint64_t) +
+                            sizeof(float) * (kHeadDim + 2 * NWARPS + NWARPS * kHeadDim + NWARPS) + 16;
+    auto kern = flb_decode_attn_kernel<CacheT, TILE_ROWS, STAGES, NWARPS>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    const unsigned grid = (unsigned)a.B * (unsigned)a.H * (unsigned)a.nsplit_max;
+    kern<<<grid, (NWARPS + 1) * 32, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_decode(const DecodeArgs &a, bool cache_f16, cudaStream_t stream) {
+    if (cache_f16) return launch_decode_t<__half, 32, 4, 4>(a, stream);
+    return launch_decode_t<float, 16, 4, 4>(a, stream);
+}
+
+} // namespace flb

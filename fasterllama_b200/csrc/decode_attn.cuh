@@ -1,0 +1,43 @@
+// decode_attn.cuh — device-side argument block shared by the decode kernels and the launch layer.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace flb {
+
+constexpr int kHeadDim = 128;          // size_per_head this build is specialised for
+constexpr int kDefaultSplitLen = 256;  // cache rows per split-KV partition
+constexpr int kStatusWords = 4;        // status header (16 B) in front of the arrival counters
+
+// Error bits a kernel may set in the status word (scratch[0]).
+enum : unsigned {
+    kErrProducerWait = 1u,  // the copy-issuing warp gave up waiting for a free stage
+    kErrConsumerWait = 2u,  // a compute warp gave up waiting for a stage to land
+};
+
+struct DecodeArgs {
+    int B, H, T;
+    int start_pos;
+    const int *past_lens;
+    int nsplit_max;  // grid holds nsplit_max CTAs per (b,h)
+    int split_len;
+    int input_mode;
+    const void *q, *k, *v;
+    const float *act_scale, *q_w_scale, *k_w_scale, *v_w_scale;
+    const float *freq_cis;
+    int rope_pos0, rope_add_past;
+    int mask_mode;
+    const float *attn_mask;
+    int mask_row_stride;
+    void *k_cache, *v_cache;
+    void *out;
+    int out_f16;
+    float scale_log2e;  // softmax_scale * log2(e)
+    unsigned *status;   // [kStatusWords]
+    unsigned *counters; // [B*H] arrivals per (b,h); zero on entry, zero on exit
+    float *part_o;      // [B*H, nsplit_max, d]
+    float *part_ml;     // [B*H, nsplit_max, 2]  (running max in the log2 domain, sum)
+};
+
+} // namespace flb

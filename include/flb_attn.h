@@ -1,0 +1,189 @@
+/*
+ * flb_attn.h — C ABI of the B200 (sm_100a) attention path for FasterLLaMA.
+ *
+ * One call replaces the whole attention section of the reference's decoder layer,
+ * OpenDecoder<OpType,INT8>::forward, fasterLlama/cuda/open_decoder.cu:138-239:
+ *
+ *   launchQKRoteEmbeddingTranspose      fasterLlama/cuda/decoder_kernels.cu:553-590
+ *   launchDequantizedVTransposeKernel   fasterLlama/cuda/decoder_kernels.cu:953-986
+ *   launchStoreKVcacheKernel            fasterLlama/cuda/decoder_kernels.cu:634-662
+ *   cublasSgemvStridedBatched / cublasGemmStridedBatchedEx  (Q.K^T)   open_decoder.cu:181-201
+ *   launchBlockSoftmaxKernel            fasterLlama/cuda/decoder_kernels.cu:837-848
+ *   cublasSgemvStridedBatched / cublasGemmStridedBatchedEx  (P.V)     open_decoder.cu:218-238
+ *
+ * Everything is plain C: pointers are device pointers unless said otherwise, sizes are
+ * ints / size_t, the stream is a cudaStream_t passed as void*.  The library allocates
+ * nothing, never synchronises the device, never exits and never throws: every entry
+ * point returns a flb_status.
+ */
+#ifndef FLB_ATTN_H
+#define FLB_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLB_ATTN_ABI_VERSION 1
+
+/* ---- status codes (0 = ok, negative = error) ------------------------------------ */
+typedef enum flb_status {
+    FLB_OK = 0,
+    FLB_ERR_NULL_POINTER = -1,      /* a required pointer is NULL                       */
+    FLB_ERR_BAD_SHAPE = -2,         /* a dimension is <= 0 or inconsistent               */
+    FLB_ERR_UNSUPPORTED = -3,       /* valid in the reference, not built here            */
+    FLB_ERR_MISALIGNED = -4,        /* a pointer or stride breaks the 16-byte rule       */
+    FLB_ERR_SCRATCH_TOO_SMALL = -5, /* scratch_bytes < flb_attn_workspace_bytes()        */
+    FLB_ERR_LAUNCH = -6,            /* the CUDA runtime refused the launch               */
+    FLB_ERR_BAD_ENUM = -7,          /* an enum field holds an unknown value              */
+    FLB_ERR_DEVICE = -8,            /* the device is not sm_100 or the driver is missing */
+    FLB_ERR_TOO_LARGE = -9          /* beyond a stated fixed maximum                     */
+} flb_status;
+
+/* ---- enums ---------------------------------------------------------------------- */
+
+/* Form of q/k/v handed to the call, all laid out [batch, seq_len, head_num, size_per_head]
+ * (the row-major output of the QKV GEMMs, open_decoder.cu:105-136). */
+typedef enum flb_input_mode {
+    FLB_IN_INT32 = 0, /* int32 accumulators; value = float(acc) * act_scale[b*S+s] * w_scale[h*d+i],
+                         multiplied in that order (decoder_kernels.cu:449, :875)            */
+    FLB_IN_F32 = 1,   /* float values, no scales                                            */
+    FLB_IN_F16 = 2    /* half values, no scales                                             */
+} flb_input_mode;
+
+typedef enum flb_dtype {
+    FLB_F32 = 0,
+    FLB_F16 = 1
+} flb_dtype;
+
+/* The reference takes an additive fp32 mask [total_len, total_len] from the caller
+ * (DecoderInitParam::attn_mask, open_decoder.h:16) and adds mask[start_pos + q][k] to the
+ * scaled score (decoder_kernels.cu:807-815).  GENERIC does exactly that.  The CAUSAL modes
+ * compute the same thing from indices for the two masks the reference's programs build:
+ * strict (key < query position: samples/llama_fp16.cu:73-81) and inclusive
+ * (key <= query position).  A query row whose keys are all masked returns zeros. */
+typedef enum flb_mask_mode {
+    FLB_MASK_NONE = 0,
+    FLB_MASK_GENERIC = 1,
+    FLB_MASK_CAUSAL_INCLUSIVE = 2,
+    FLB_MASK_CAUSAL_STRICT = 3
+} flb_mask_mode;
+
+/* ---- the parameter block -------------------------------------------------------- */
+typedef struct flb_attn_params {
+    /* dimensions (names follow OpenDecoder's constructor, open_decoder.h:65) */
+    int batch_size;    /* B                                                              */
+    int head_num;      /* H                                                              */
+    int size_per_head; /* d; this build supports 128                                     */
+    int seq_len;       /* S, tokens of this call per sequence: 1 = decode, >1 = prefill  */
+    int start_pos;     /* rows already in the cache, same for every sequence
+                          (OpenDecoder::forward's start_pos)                             */
+    int total_len;     /* T, row capacity of one (b,h) cache slab                        */
+
+    /* Optional extension the reference lacks: per-sequence cached rows, device int[B].
+     * When non-NULL it replaces start_pos (decode only); max_past_len is then the host's
+     * upper bound on its entries (0 = total_len - 1) and only sizes the grid. */
+    const int *past_lens;
+    int max_past_len;
+
+    /* inputs */
+    int input_mode;         /* flb_input_mode                                            */
+    const void *q;          /* [B,S,H,d]                                                 */
+    const void *k;          /* [B,S,H,d]                                                 */
+    const void *v;          /* [B,S,H,d]                                                 */
+    const float *act_scale; /* FLB_IN_INT32: [B*S] per-token activation scale            */
+    const float *q_w_scale; /* FLB_IN_INT32: [H*d] per-output-channel weight scales      */
+    const float *k_w_scale;
+    const float *v_w_scale;
+
+    /* RoPE: table rows of d floats, [2i] = cos, [2i+1] = sin (decoding_kernels.cu:85-114);
+     * pairs (2i, 2i+1) are rotated (decoder_kernels.cu:455-458).  Token s of sequence b uses
+     * row rope_pos0 + s (+ its cached-row count when rope_add_past != 0).  The reference
+     * always uses row s of the pointer it is given (decoder_kernels.cu:440), i.e.
+     * rope_pos0 = 0, rope_add_past = 0.  NULL table = no rotation. */
+    const float *freq_cis;
+    int rope_pos0;
+    int rope_add_past;
+
+    /* mask */
+    int mask_mode;           /* flb_mask_mode                                            */
+    const float *attn_mask;  /* GENERIC: row 0 of the caller's [T,T] mask (NOT offset by
+                                start_pos; the call adds the query position itself)      */
+    int mask_row_stride;     /* GENERIC: floats between mask rows (the reference: T)     */
+
+    /* KV cache, [B,H,T,d] (open_decoder.h:72-77); rows [past, past+S) are written by the
+     * call.  The reference's cache is fp32; fp16 halves the decode traffic and is legal
+     * because nothing but attention reads the cache. */
+    void *k_cache;
+    void *v_cache;
+    int cache_dtype;         /* flb_dtype                                                */
+
+    /* output [B,H,S,d] (qkv_buf_, open_decoder.h:61) */
+    void *out;
+    int out_dtype;           /* flb_dtype; the reference's is fp32                       */
+
+    float softmax_scale;     /* the reference passes rsqrtf(d) (open_decoder.cu:208)     */
+
+    /* Scratch for the split-KV partial results (decode) — the reference's qk_buf_ is free
+     * for this.  scratch_zeroed != 0 promises that the first
+     * flb_attn_counter_bytes() bytes are zero on entry (they are left zero on exit), which
+     * saves one memset node per call. */
+    void *scratch;
+    size_t scratch_bytes;
+    int scratch_zeroed;
+
+    /* rows of one split-KV partition; 0 = default (256).  Results depend on this value
+     * and on each sequence's own length only — never on B, H, the GPU count or the grid. */
+    int split_len;
+} flb_attn_params;
+
+/* ---- entry points --------------------------------------------------------------- */
+
+/* ABI version of the loaded library (== FLB_ATTN_ABI_VERSION it was built with). */
+int flb_attn_abi_version(void);
+
+/* Text for a status code; never NULL. */
+const char *flb_status_string(int status);
+
+/* Bytes of scratch the decode call needs for these dimensions (host computation only).
+ * Replaces the qk_buf_ term of OpenDecoder::getWorkspaceSize (open_decoder.cu:54-68). */
+int flb_attn_workspace_bytes(const flb_attn_params *p, size_t *bytes_out);
+
+/* Bytes at the start of scratch that hold the split arrival counters. */
+int flb_attn_counter_bytes(const flb_attn_params *p, size_t *bytes_out);
+
+/* Host-side argument check only (no CUDA call); the launch entry points run it first. */
+int flb_attn_validate(const flb_attn_params *p);
+
+/* Decode: seq_len == 1.  Replaces open_decoder.cu:142-171 (dequant, RoPE, transpose, cache
+ * append) + :194-201 (K.q) + :207-208 (softmax) + :231-238 (P.V) with one kernel launch. */
+int flb_attn_decode(const flb_attn_params *p, void *cuda_stream);
+
+/* Prefill: seq_len > 1, start_pos == 0 (the reference attends over the fresh K/V only,
+ * open_decoder.cu:181-190, so it is valid for start_pos == 0 only).  Replaces :142-171 +
+ * :181-190 + :207-208 + :218-227. */
+int flb_attn_prefill(const flb_attn_params *p, void *cuda_stream);
+
+/* Picks decode or prefill from seq_len exactly like open_decoder.cu:179,216. */
+int flb_attn_forward(const flb_attn_params *p, void *cuda_stream);
+
+/* Looks at a caller-built additive mask (device fp32 [rows, row_stride]) and reports which
+ * flb_mask_mode reproduces it: CAUSAL_STRICT, CAUSAL_INCLUSIVE, NONE (all zero) or GENERIC.
+ * A masked entry counts as such only when it is <= -1e30 (the samples use -FLT_MAX), because a
+ * milder value such as -1e5 does not drop a key when the whole row is masked.
+ * `scratch16` is 16 bytes of device memory the check may overwrite.  Synchronises the stream
+ * (it copies the verdict to the host): call it once at set-up, never per step. */
+int flb_attn_classify_mask(const float *attn_mask, int rows, int row_stride, void *scratch16,
+                           int *mode_out, void *cuda_stream);
+
+/* Reads the kernels' error word at the head of `scratch` into *status_out (0 = no kernel gave
+ * up on a bounded wait or met a cache length outside [0, total_len-1]).  Synchronises the
+ * stream.  The reference has no counterpart: its kernels cannot report anything. */
+int flb_attn_scratch_status(const void *scratch, unsigned *status_out, void *cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLB_ATTN_H */

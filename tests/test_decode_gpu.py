@@ -1,0 +1,132 @@
+"""Parity of the CUDA decode attention (through the C ABI) against the host oracle."""
+import numpy as np
+import pytest
+
+from fasterllama_b200 import attention as A
+from fasterllama_b200 import workloads as W
+
+from util import FP16_ABS, assert_abs_close, assert_fp32_close, run_cuda, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+# every tile (16/32 rows) and split (256 rows) boundary, +-1
+LENGTHS = [0, 1, 2, 15, 16, 17, 31, 32, 33, 127, 128, 129, 255, 256, 257, 300, 511, 512, 513, 700]
+
+
+def _check(case, cuda, orc, fp16):
+    assert cuda["status"] == 0, f"kernel status word {cuda['status']:#x}"
+    if fp16:
+        assert_abs_close(cuda["out"], orc["out"].astype(np.float32), FP16_ABS, case.name + " out")
+    else:
+        assert_fp32_close(cuda["out"], orc["out"], what=case.name + " out")
+    # the appended rows are bit-exact (same dequant/RoPE arithmetic up to fma contraction -> 1e-6),
+    # every other cache row is untouched
+    kc, ko = cuda["k_cache"], orc["k_cache"].astype(np.float32)
+    vc, vo = cuda["v_cache"], orc["v_cache"].astype(np.float32)
+    tol = 2e-3 if fp16 else 1e-5
+    assert np.abs(kc - ko).max() <= tol * max(1.0, np.abs(ko).max())
+    assert np.array_equal(vc, vo), "V cache differs (append is a pure copy/round)"
+
+
+@pytest.mark.parametrize("past", LENGTHS)
+def test_fp32_decode_lengths(cuda_device, past):
+    case = W.host_case(f"fp32-L{past}", 100 + past, 1, 4, 768, past=past)
+    _check(case, run_cuda(case), run_oracle(case), fp16=False)
+
+
+@pytest.mark.parametrize("past", LENGTHS)
+def test_fp16_decode_lengths(cuda_device, past):
+    case = W.host_case(f"fp16-L{past}", 200 + past, 2, 4, 768, past=past, in_dtype="float16",
+                       cache_dtype="float16", out_dtype="float16")
+    _check(case, run_cuda(case), run_oracle(case), fp16=True)
+
+
+@pytest.mark.parametrize("mask_mode", [A.FLB_MASK_NONE, A.FLB_MASK_GENERIC, A.FLB_MASK_CAUSAL_INCLUSIVE, A.FLB_MASK_CAUSAL_STRICT])
+@pytest.mark.parametrize("past", [0, 5, 300])
+def test_mask_modes(cuda_device, mask_mode, past):
+    case = W.host_case(f"mask{mask_mode}-L{past}", 300 + past, 2, 4, 400, past=past, mask_mode=mask_mode)
+    cuda, orc = run_cuda(case), run_oracle(case)
+    _check(case, cuda, orc, fp16=False)
+    if mask_mode == A.FLB_MASK_CAUSAL_STRICT and past == 0:
+        # the only key is the token itself and it is masked: the row is fully masked -> zeros
+        assert not cuda["out"].any()
+
+
+def test_int32_inputs_with_scales(cuda_device):
+    """The reference's post-GEMM form: int32 accumulators, per-token and per-channel scales."""
+    case = W.host_case("int32", 7, 3, 8, 600, past=411, in_dtype="int32")
+    _check(case, run_cuda(case), run_oracle(case), fp16=False)
+
+
+def test_reference_rope_row(cuda_device):
+    """The reference rotates a decode token with table row 0 of the pointer it is given."""
+    case = W.host_case("rope-ref", 8, 2, 4, 300, past=200, rope="reference")
+    _check(case, run_cuda(case), run_oracle(case), fp16=False)
+    case = W.host_case("rope-none", 9, 2, 4, 300, past=200, rope="none")
+    _check(case, run_cuda(case), run_oracle(case), fp16=False)
+
+
+def test_per_sequence_lengths(cuda_device):
+    lens = np.array([0, 1, 255, 256, 257, 1000, 513, 31], dtype=np.int32)
+    case = W.host_case("ragged", 11, 8, 4, 1100, past=lens, in_dtype="float16", cache_dtype="float16", out_dtype="float32")
+    _check(case, run_cuda(case), run_oracle(case), fp16=True)
+
+
+def test_config1_fp32_llama7b_layer(cuda_device):
+    """fp32, batch 1, 32 heads x 128, cache 256, RoPE at position 256, seed 0."""
+    case = W.host_case("config1", 0, 1, 32, 512, past=256)
+    cuda, orc = run_cuda(case), run_oracle(case)
+    _check(case, cuda, orc, fp16=False)
+
+
+def test_config2_fp16_llama7b_full_size(cuda_device):
+    """fp16, batch 16, 32 heads x 128, lengths uniform in [1024, 2048], seed 1 — full size."""
+    lens = W.draw_lengths(1, 16, 1024, 2048)
+    case = W.host_case("config2", 1, 16, 32, 2049, past=lens, in_dtype="float16", cache_dtype="float16", out_dtype="float16")
+    _check(case, run_cuda(case), run_oracle(case), fp16=True)
+
+
+def test_split_len_and_repeat_calls(cuda_device):
+    """Other split sizes give results within tolerance of each other; repeating the call on the
+    same scratch (counters must have been left at zero) is bit-identical."""
+    base = W.host_case("split", 21, 2, 4, 1200, past=1100)
+    orc = run_oracle(base)
+    outs = []
+    for sl in (64, 128, 256, 512):
+        case = W.host_case("split", 21, 2, 4, 1200, past=1100, split_len=sl)
+        cuda = run_cuda(case)
+        _check(case, cuda, orc, fp16=False)
+        outs.append(cuda["out"])
+    import torch
+    case = W.host_case("split", 21, 2, 4, 1200, past=1100)
+    r = run_cuda(case, calls=1)
+    dev = r["dev"]
+    p = case.params(dev)
+    first = dev["out"].clone()
+    for _ in range(3):
+        A.forward(p)
+    torch.cuda.synchronize()
+    assert torch.equal(first, dev["out"])
+    case.scratch_zeroed = True  # counters were left at zero by the calls above
+    A.forward(case.params(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(first, dev["out"])
+
+
+def test_head_sharding_is_bit_identical(cuda_device):
+    """Running a subset of the (b,h) units alone gives the same bits as running them in the full
+    batch: the split partition depends on each sequence's length only."""
+    import torch
+    lens = np.array([700, 300, 1024, 77], dtype=np.int32)
+    full = W.host_case("shard-full", 31, 4, 8, 1100, past=lens)
+    out_full = run_cuda(full)["out"]
+    for hs in (slice(0, 4), slice(4, 8)):
+        part = W.host_case("shard-full", 31, 4, 8, 1100, past=lens)
+        a = part.arrays
+        for n in ("q", "k", "v"):
+            a[n] = np.ascontiguousarray(a[n][:, :, hs])
+        for n in ("k_cache", "v_cache", "out"):
+            a[n] = np.ascontiguousarray(a[n][:, hs])
+        part.H = 4
+        got = run_cuda(part)["out"]
+        assert np.array_equal(got, out_full[:, hs])
