@@ -1,0 +1,450 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-attention hot path (one JSON line on stdout, rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c4]
+
+A step is one decode-attention call (one new token per sequence, one decoder layer) over one batch
+of synthetic input: by default fp16, batch 16, 32 heads x 128, cached lengths uniform in
+[1024, 2048] drawn from seed 1 (the LLaMA-2-7B layer shape the metric is quoted on).  With N > 1
+every rank runs its own batch of that shape (independent (batch, head) units, no collective on the
+data path: weak scaling) and the value is the sum over ranks divided by the slowest rank's time.
+
+`value`   algorithmic bytes (K and V rows read + appended rows + q/k/v + output; no mask, score or
+          table bytes) per second with all inputs resident in HBM; four distinct input sets are
+          rotated so no step re-reads what the previous steps left in L2.
+`e2e`     the same metric through the public call with HOST inputs: every step copies that step's
+          q, k, v from pinned host memory, runs the call, and reads the output back.
+`roofline` the decode kernel's bytes per launch over its average duration (CUDA events on the
+          launching stream), against the measured copy bandwidth of this pool's B200s.
+`cpu_baseline` the scalar host oracle timed on this box's cores on a bounded sample.
+
+`--impl reference` times the reference's own CUDA attention chain (three kernels + two cuBLAS gemv
++ softmax, fp32 cache) built from the reference checkout by oracle/build_ref.sh; the reference has
+no CPU implementation of this path.  Its decode gemv arguments are corrected as described in
+oracle/ref_runner.cu (as written they are rejected by cuBLAS for L > 128), and since it has one
+cached length per call the ragged batch is run as one call per sequence.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+NBUF = 4  # distinct input sets rotated through the timed loop (--sets)
+
+WORKLOADS = {
+    # name: (B, H, lo, hi, seed, description)
+    "c2": (16, 32, 1024, 2048, 1, "fp16 decode attention, LLaMA-2-7B layer shape: batch 16, 32 heads x 128, cached lengths U[1024,2048], seed 1"),
+    "c4": (64, 40, 2048, 4096, 3, "fp16 decode attention, LLaMA-2-13B layer shape: batch 64, 40 heads x 128, cached lengths U[2048,4096], seed 3"),
+}
+
+
+def load_peaks() -> tuple[float, str]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.005):
+        self.samples: list[tuple[int, int]] = []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thr = None
+        self.err = None
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # NVML missing: report it, do not fail the benchmark
+            self.nv = None
+            self.err = repr(e)
+        self.period = period_s
+
+    def _one(self):
+        nv = self.nv
+        try:
+            mhz = int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+            try:
+                reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+            except Exception:
+                reasons = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+            self.samples.append((mhz, reasons))
+        except Exception as e:
+            self.err = repr(e)
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._one()
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self.nv is None:
+            return
+        self._stop.clear()
+        self._thr = threading.Thread(target=self._run, daemon=True)
+        self._thr.start()
+
+    def stop(self):
+        if self._thr is not None:
+            self._one()
+            self._stop.set()
+            self._thr.join()
+            self._thr = None
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "error": self.err}
+        mhz = sorted(s[0] for s in self.samples)
+        bits = 0
+        for _, r in self.samples:
+            bits |= r
+        names = {
+            0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+            0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+            0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+        }
+        reasons = [n for b, n in names.items() if bits & b and n != "gpu_idle"]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(mhz)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local):
+    from fasterllama_b200 import attention as A
+    from fasterllama_b200 import workloads as W
+
+    global NBUF
+    NBUF = max(1, args.sets)
+    B, H, lo, hi, seed, desc = WORKLOADS[args.workload]
+    T = hi + 1
+    dev = f"cuda:{local}"
+    lens = W.draw_lengths(seed, B, lo, hi)  # the same lengths on every rank and in every set
+    sets = []
+    for j in range(NBUF):
+        c = W.device_case(f"{args.workload}-{j}", seed + 7919 * j + 104729 * rank, B, H, T, lens, device=dev)
+        c.scratch_zeroed = True  # device_case hands over zeroed scratch; the kernel leaves it zeroed
+        sets.append((c, c.params()))
+    bytes_step = sets[0][0].algorithmic_bytes()
+    stream = torch.cuda.current_stream()
+
+    def step(i):
+        A.decode(sets[i % NBUF][1], stream)
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    sampler.start()
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    sampler.stop()
+    t_dev = e0.elapsed_time(e1) * 1e-3
+    barrier(world)
+    t = max_over_ranks(t_dev, world)
+    for c, _ in sets:
+        assert A.scratch_status(c.arrays["scratch"]) == 0, "a decode kernel reported an error status"
+
+    # ---- end to end: host q/k/v in, output back on the host, every step --------------------------
+    host_in = []
+    for c, _ in sets:
+        host_in.append({n: c.arrays[n].cpu().pin_memory() for n in ("q", "k", "v")})
+    host_out = torch.empty_like(sets[0][0].arrays["out"], device="cpu").pin_memory()
+    h2d = sum(host_in[0][n].numel() * host_in[0][n].element_size() for n in ("q", "k", "v"))
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step(i):
+        c, p = sets[i % NBUF]
+        for n in ("q", "k", "v"):
+            c.arrays[n].copy_(host_in[i % NBUF][n], non_blocking=True)
+        A.decode(p, stream)
+        host_out.copy_(c.arrays["out"], non_blocking=True)
+        stream.synchronize()  # the caller reads the step's result before it issues the next step
+
+    for i in range(max(args.warmup, 3)):
+        e2e_step(i)
+    barrier(world)
+    e0.record(stream)
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t_e2e = max_over_ranks(e0.elapsed_time(e1) * 1e-3, world)
+    barrier(world)
+
+    peak, peak_src = load_peaks()
+    total_bytes = sum_over_ranks(float(bytes_step), world)
+    value = total_bytes * args.steps / t / 1e9
+    e2e_val = total_bytes * args.steps / t_e2e / 1e9
+    achieved = bytes_step * args.steps / t_dev / 1e9  # this rank's kernel: one launch per step
+
+    line = {
+        "metric": "decode_attn_hbm_gbps", "value": round(value, 1), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(t / args.steps * 1e3, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 storage, f32 arithmetic", "data": "synthetic",
+        "config": {
+            "workload": desc, "per_gpu_batch": B, "heads": H, "head_dim": 128, "cache_rows_total": int(lens.sum()),
+            "total_len": T, "split_len": 512, "l2": f"{NBUF} distinct input sets rotated ({NBUF * bytes_step / 1e6:.0f} MB > 126 MB L2), no flush kernel in the timed region",
+            "sharding": "independent (batch, head) units per rank, no collective",
+        },
+        "tokens_per_s": round(B * world * args.steps / t, 1),
+        "pct_of_8TBps": round(100 * value / world / 8000.0, 2),
+        "bytes_per_step_per_gpu": bytes_step,
+        "gpu_launches": args.steps,
+        "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": round(t_e2e / args.steps * 1e3, 5), "tokens_per_s": round(B * world * args.steps / t_e2e, 1)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "peak_source": f"{peak_src} (copy bandwidth, MEASURED_PEAKS.json)",
+                     "kernel": "flb_decode_attn_kernel<__half,...>", "traffic": DRAM_TRAFFIC_PER_LAUNCH.get(args.workload)},
+        "clocks": sampler.summary(),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(sets[0][0], bytes_step, B)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch, from the ncu capture summarised
+# under profiles/ (None until a capture of that workload exists)
+DRAM_TRAFFIC_PER_LAUNCH: dict[str, int | None] = {"c2": None, "c4": None}
+
+
+def cpu_baseline(case, bytes_step: int, B: int, min_seconds: float = 10.0) -> dict:
+    """The host oracle (a scalar port: the reference has no CPU path) on all host cores, on a
+    bounded sample: the first 4 sequences of the batch, repeated for about `min_seconds`."""
+    from oracle import oracle
+
+    nb = min(4, B)
+    host = {}
+    for k, v in case.arrays.items():
+        if k == "scratch":
+            continue
+        a = v.cpu().numpy()
+        host[k] = np.ascontiguousarray(a[:nb]) if k in ("q", "k", "v", "k_cache", "v_cache", "out", "past_lens") else a
+    import copy
+
+    sub = copy.copy(case)
+    sub.B = nb
+    sub.arrays = host
+    p = sub.params(host)
+    sub_bytes = sub.algorithmic_bytes()
+    threads = oracle.set_threads(oracle.hw_threads())
+    oracle.attention(p)  # warm
+    n, t0 = 0, time.perf_counter()
+    while True:
+        oracle.attention(p)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds:
+            break
+    return {"value": round(sub_bytes * n / dt / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+            "tokens_per_s": round(nb * n / dt, 2),
+            "sample": f"first {nb} of {B} sequences of the same batch, {n} repetitions in {dt:.1f} s, OpenMP over (batch, head)"}
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference(args, rank, world, local):
+    if rank != 0:
+        return
+    from oracle import ref_runner
+
+    if not ref_runner.available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libflb_ref.so was not built (the reference checkout was absent at build time)"}), flush=True)
+        return
+    from fasterllama_b200 import workloads as W
+
+    B, H, lo, hi, seed, desc = WORKLOADS[args.workload]
+    T, d = hi + 1, 128
+    dev = f"cuda:{local}"
+    lens = W.draw_lengths(seed, B, lo, hi)
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    ref = ref_runner.RefRunner()
+    mask = torch.from_numpy(W.causal_mask(T, strict=False)).to(dev)
+    table = ref.freq_cis(T + 8)
+    nbuf = 2
+    sets = []
+    for j in range(nbuf):
+        per_seq = []
+        kc = torch.randn((B, H, T, d), generator=g, device=dev, dtype=torch.float32)
+        vc = torch.randn((B, H, T, d), generator=g, device=dev, dtype=torch.float32)
+        qkv = {n: torch.randint(-8192, 8192, (B, 1, H, d), generator=g, device=dev, dtype=torch.int32) for n in ("q", "k", "v")}
+        out = torch.zeros((B, H, 1, d), device=dev, dtype=torch.float32)
+        for b in range(B):  # one cached length per call in the reference: one call per sequence
+            t = {n: qkv[n][b:b + 1] for n in ("q", "k", "v")}
+            t.update(act_scale=torch.full((1,), 2.0**-7, device=dev), q_w_scale=torch.full((H * d,), 2.0**-6, device=dev),
+                     k_w_scale=torch.full((H * d,), 2.0**-6, device=dev), v_w_scale=torch.full((H * d,), 2.0**-6, device=dev),
+                     freq_cis=table, attn_mask=mask, k_cache=kc[b:b + 1], v_cache=vc[b:b + 1], out=out[b:b + 1])
+            per_seq.append(ref.make_args(t, start_pos=int(lens[b]), rope_row=int(lens[b])))
+        sets.append((per_seq, qkv, out))
+    stream = torch.cuda.current_stream()
+
+    def step(i):
+        for a in sets[i % nbuf][0]:
+            st = ref.attention(a, stream.cuda_stream)
+            if st != 0:
+                raise RuntimeError(f"reference runner status {st}")
+
+    steps = args.steps
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    sampler.start()
+    e0.record(stream)
+    for i in range(steps):
+        step(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    sampler.stop()
+    t = e0.elapsed_time(e1) * 1e-3
+
+    host_in = [{n: s[1][n].cpu().pin_memory() for n in ("q", "k", "v")} for s in sets]
+    host_out = torch.empty_like(sets[0][2], device="cpu").pin_memory()
+    h2d = sum(v.numel() * v.element_size() for v in host_in[0].values())
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step(i):
+        s = sets[i % nbuf]
+        for n in ("q", "k", "v"):
+            s[1][n].copy_(host_in[i % nbuf][n], non_blocking=True)
+        step(i)
+        host_out.copy_(s[2], non_blocking=True)
+        stream.synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for i in range(steps):
+        e2e_step(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t_e2e = e0.elapsed_time(e1) * 1e-3
+
+    # same byte basis as the other arm (the fp16 workload's algorithmic bytes), so that the ratio of
+    # the two lines is a ratio of times; the reference itself moves more (fp32 cache, score round trips)
+    e_c, e_io = 2, 2
+    bytes_step = int(H * (2 * lens.astype(np.int64) * d * e_c + 2 * d * e_c + 3 * d * e_io + d * e_io).sum())
+    value = bytes_step * steps / t / 1e9
+    e2e_val = bytes_step * steps / t_e2e / 1e9
+    line = {
+        "impl": "reference", "metric": "decode_attn_hbm_gbps", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1,
+        "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": round(t / steps * 1e3, 5), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc, "reference_mode": "the reference's kernels + cuBLAS gemv with corrected arguments (as written cuBLAS rejects them for L > 128), fp32 cache, one call per sequence (it has one cached length per call)",
+                   "byte_basis": "fp16 workload bytes, identical to the other arm"},
+        "tokens_per_s": round(B * steps / t, 1),
+        "gpu_launches": steps * B * 6,
+        "cpu_baseline": {"value": round(value, 1), "unit": "GB/s", "cores": 0, "kind": "reference",
+                         "sample": "the whole batch; the reference has no CPU implementation of this path, so its own CUDA kernels run on the GPU"},
+        "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": round(t_e2e / steps * 1e3, 5), "tokens_per_s": round(B * steps / t_e2e, 1)},
+        "clocks": sampler.summary(),
+    }
+    print(json.dumps(line), flush=True)
+    ref.close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the host-oracle baseline leg")
+    ap.add_argument("--sets", type=int, default=NBUF, help="distinct input sets rotated through the loop (1 for a small profiler capture)")
+    args = ap.parse_args()
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU: there is no CPU path to measure")
+    torch.cuda.set_device(local)
+    if args.impl == "reference":
+        world = 1  # rank 0 alone runs the reference arm; the other ranks leave without work
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    try:
+        if args.impl == "reference":
+            run_reference(args, rank, world, local)
+        else:
+            from fasterllama_b200 import _lib
+
+            _lib.load_library()  # no fallback: fail here if the CUDA library is missing
+            run_ours(args, rank, world, local)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

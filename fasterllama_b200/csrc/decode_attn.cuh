@@ -7,7 +7,7 @@
 namespace flb {
 
 constexpr int kHeadDim = 128;          // size_per_head this build is specialised for
-constexpr int kDefaultSplitLen = 256;  // cache rows per split-KV partition
+constexpr int kDefaultSplitLen = 512;  // cache rows per split-KV partition
 constexpr int kStatusWords = 4;        // status header (16 B) in front of the arrival counters
 
 // Error bits a kernel may set in the status word (scratch[0]).

@@ -134,7 +134,7 @@ typedef struct flb_attn_params {
     size_t scratch_bytes;
     int scratch_zeroed;
 
-    /* rows of one split-KV partition; 0 = default (256).  Results depend on this value
+    /* rows of one split-KV partition; 0 = default (512).  Results depend on this value
      * and on each sequence's own length only — never on B, H, the GPU count or the grid. */
     int split_len;
 } flb_attn_params;

@@ -104,7 +104,7 @@ def test_workspace_grows_with_cache_capacity_and_covers_the_counters():
     small = A.workspace_bytes(2, 4, 257)
     big = A.workspace_bytes(2, 4, 4097)
     assert big > small > A.counter_bytes(2, 4) >= 16 + 4 * 8
-    assert A.workspace_bytes(2, 4, 4097, split_len=512) < big
+    assert A.workspace_bytes(2, 4, 4097, split_len=1024) < big < A.workspace_bytes(2, 4, 4097, split_len=256)
 
 
 def test_status_strings():

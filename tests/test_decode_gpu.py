@@ -9,8 +9,8 @@ from util import FP16_ABS, assert_abs_close, assert_fp32_close, run_cuda, run_or
 
 pytestmark = pytest.mark.gpu
 
-# every tile (16/32 rows) and split (256 rows) boundary, +-1
-LENGTHS = [0, 1, 2, 15, 16, 17, 31, 32, 33, 127, 128, 129, 255, 256, 257, 300, 511, 512, 513, 700]
+# every tile (16/32 rows) and split (512 rows) boundary, +-1
+LENGTHS = [0, 1, 2, 15, 16, 17, 31, 32, 33, 63, 64, 65, 255, 256, 257, 511, 512, 513, 700, 1024, 1025]
 
 
 def _check(case, cuda, orc, fp16):
@@ -30,13 +30,13 @@ def _check(case, cuda, orc, fp16):
 
 @pytest.mark.parametrize("past", LENGTHS)
 def test_fp32_decode_lengths(cuda_device, past):
-    case = W.host_case(f"fp32-L{past}", 100 + past, 1, 4, 768, past=past)
+    case = W.host_case(f"fp32-L{past}", 100 + past, 1, 4, 1100, past=past)
     _check(case, run_cuda(case), run_oracle(case), fp16=False)
 
 
 @pytest.mark.parametrize("past", LENGTHS)
 def test_fp16_decode_lengths(cuda_device, past):
-    case = W.host_case(f"fp16-L{past}", 200 + past, 2, 4, 768, past=past, in_dtype="float16",
+    case = W.host_case(f"fp16-L{past}", 200 + past, 2, 4, 1100, past=past, in_dtype="float16",
                        cache_dtype="float16", out_dtype="float16")
     _check(case, run_cuda(case), run_oracle(case), fp16=True)
 
