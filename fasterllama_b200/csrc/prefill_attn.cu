@@ -1,5 +1,574 @@
-// prefill_attn.cu — causal prefill attention (placeholder until the tensor-core kernel lands).
+// prefill_attn.cu — causal prefill attention (seq_len > 1, empty cache) for sm_100a.
+//
+// Replaces, for seq_len > 1, the reference's chain
+//   warpQKRoteEmbeddingTransposeKernel   fasterLlama/cuda/decoder_kernels.cu:425-464
+//   warpDequantizedVTransposeKernel      fasterLlama/cuda/decoder_kernels.cu:858-884
+//   storeKVcacheKernel                   fasterLlama/cuda/decoder_kernels.cu:597-611
+//   cublasGemmStridedBatchedEx (Q.K^T)   fasterLlama/cuda/open_decoder.cu:181-190
+//   blockSoftmaxKernel                   fasterLlama/cuda/decoder_kernels.cu:800-835
+//   cublasGemmStridedBatchedEx (P.V)     fasterLlama/cuda/open_decoder.cu:218-227
+// with two launches:
+//
+// 1. flb_prefill_prologue_kernel — one streaming pass: dequantise q,k,v, rotate q,k (RoPE),
+//    transpose [B,S,H,d] -> [B,H,S,d], append k,v to the caches (rows 0..S-1) and leave fp16
+//    copies of Q (and of K,V when the cache is fp32) for the tensor cores.
+//
+// 2. flb_prefill_attn_kernel — flash attention on the 5th-generation tensor cores.  One CTA per
+//    (b,h, 128-query tile); K/V tiles of 128 keys.  Warp roles:
+//      warp 0      TMA producer: Q once, then K_j / V_j boxes (128-byte swizzle) into a 2-stage ring
+//      warp 1      allocates TMEM and issues tcgen05.mma:  S_j = Q.K_j^T  (fp16 x fp16 -> fp32 in TMEM,
+//                  two S buffers)  and  O += P_j.V_j  (P from shared memory, V as an MN-major operand)
+//      warps 2-5   one thread per query row: tcgen05.ld S, scale + mask, online softmax in the log2
+//                  domain, P_j as fp16 into swizzled shared memory; O in TMEM is rescaled only when a
+//                  row's maximum grew by more than 2^8 (exact: the final division uses the same
+//                  reference maximum); epilogue O / l -> global.
+//    All hand-offs are mbarriers (TMA transaction counts, tcgen05.commit, thread arrivals); every
+//    wait is bounded by a wall-clock budget and reports through the status word instead of hanging.
+//    Causal modes skip the key tiles above the diagonal.  TMEM: 512 columns (S0, S1, O).
 #include "prefill_attn.cuh"
+
+#include "flb_ptx.cuh"
+
+#include <cuda_fp16.h>
+
 namespace flb {
-int launch_prefill(const flb_attn_params *, cudaStream_t) { return FLB_ERR_UNSUPPORTED; }
+
+namespace {
+
+constexpr int D = 128;       // head dimension
+constexpr int BM = 128;      // query rows per CTA
+constexpr int KV_STAGES = 2;
+constexpr int Q_TILE_BYTES = BM * D * 2; // 128 x 128 fp16 = 32 KB, two [128 x 64] swizzled blocks
+constexpr int NUM_THREADS = 192;
+constexpr int kKeysPerTile = 64;         // BN: 112 KB of shared memory and 256 TMEM columns per CTA -> 2 CTAs per SM
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f; // log2 domain: P stays below 2^8, exact in fp16 range
+
+enum : unsigned { kErrPrefillWait = 8u, kErrPrefillAlign = 16u };
+
+struct PrefillArgs {
+    int B, H, S, T;
+    int input_mode;
+    const void *q, *k, *v;
+    const float *act_scale, *q_w_scale, *k_w_scale, *v_w_scale;
+    const float *freq_cis;
+    int rope_pos0;
+    void *k_cache, *v_cache;
+    int cache_f16;
+    __half *qh, *kh, *vh; // fp16 staging [B,H,S,d]; kh/vh only with an fp32 cache
+    int mask_mode;
+    const float *attn_mask;
+    int mask_row_stride;
+    void *out;
+    int out_f16;
+    float scale_log2e;
+    unsigned *status;
+};
+
+// ------------------------------------------------------------------------------------------------
+// prologue
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void load8(const PrefillArgs &a, const void *base, const float *w_scale, size_t off, int b_s, int h,
+                                      int c, float (&x)[8]) {
+    if (a.input_mode == 0) {
+        // float(acc) * act_scale * w_scale, in this order (decoder_kernels.cu:449, :875)
+        const int4 lo = __ldg(reinterpret_cast<const int4 *>((const int32_t *)base + off));
+        const int4 hi = __ldg(reinterpret_cast<const int4 *>((const int32_t *)base + off) + 1);
+        const float as = __ldg(a.act_scale + b_s);
+        const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w_scale + (size_t)h * D + c * 8));
+        const float4 w1 = __ldg(reinterpret_cast<const float4 *>(w_scale + (size_t)h * D + c * 8) + 1);
+        x[0] = (float)lo.x * as * w0.x;
+        x[1] = (float)lo.y * as * w0.y;
+        x[2] = (float)lo.z * as * w0.z;
+        x[3] = (float)lo.w * as * w0.w;
+        x[4] = (float)hi.x * as * w1.x;
+        x[5] = (float)hi.y * as * w1.y;
+        x[6] = (float)hi.z * as * w1.z;
+        x[7] = (float)hi.w * as * w1.w;
+    } else if (a.input_mode == 1) {
+        const float4 lo = __ldg(reinterpret_cast<const float4 *>((const float *)base + off));
+        const float4 hi = __ldg(reinterpret_cast<const float4 *>((const float *)base + off) + 1);
+        x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+        x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+    } else {
+        const uint4 u = __ldg(reinterpret_cast<const uint4 *>((const __half *)base + off));
+        const __half2 *hp = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 t = __half22float2(hp[i]);
+            x[2 * i] = t.x;
+            x[2 * i + 1] = t.y;
+        }
+    }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
+    uint4 u;
+    __half2 *hp = reinterpret_cast<__half2 *>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) hp[i] = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+    return u;
+}
+
+__device__ __forceinline__ void store_cache8(const PrefillArgs &a, void *cache, size_t off, const float (&x)[8]) {
+    if (a.cache_f16) {
+        *reinterpret_cast<uint4 *>((__half *)cache + off) = pack8(x);
+    } else {
+        float4 *p = reinterpret_cast<float4 *>((float *)cache + off);
+        p[0] = make_float4(x[0], x[1], x[2], x[3]);
+        p[1] = make_float4(x[4], x[5], x[6], x[7]);
+    }
+}
+
+// one thread per 8 consecutive head dimensions of one (b, s, h)
+__global__ void __launch_bounds__(256) flb_prefill_prologue_kernel(const PrefillArgs a) {
+    const size_t total = (size_t)a.B * a.S * a.H * 16;
+    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= total) return;
+    const int c = (int)(idx & 15);
+    const int h = (int)((idx >> 4) % a.H);
+    const int s = (int)((idx / (16 * (size_t)a.H)) % a.S);
+    const int b = (int)(idx / (16 * (size_t)a.H * a.S));
+    const size_t in_off = (((size_t)b * a.S + s) * a.H + h) * D + c * 8;
+    float q[8], k[8], v[8];
+    load8(a, a.q, a.q_w_scale, in_off, b * a.S + s, h, c, q);
+    load8(a, a.k, a.k_w_scale, in_off, b * a.S + s, h, c, k);
+    load8(a, a.v, a.v_w_scale, in_off, b * a.S + s, h, c, v);
+    if (a.freq_cis) {
+        // pairs (2i, 2i+1): x' = x cos - y sin ; y' = y cos + x sin (decoder_kernels.cu:455-458)
+        const float4 *fr = reinterpret_cast<const float4 *>(a.freq_cis + (size_t)(a.rope_pos0 + s) * D + c * 8);
+        const float4 f0 = __ldg(fr), f1 = __ldg(fr + 1);
+        const float cs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            const float co = cs[i], sn = cs[i + 1];
+            const float qx = q[i], qy = q[i + 1], kx = k[i], ky = k[i + 1];
+            q[i] = qx * co - qy * sn;
+            q[i + 1] = qy * co + qx * sn;
+            k[i] = kx * co - ky * sn;
+            k[i + 1] = ky * co + kx * sn;
+        }
+    }
+    const size_t bh = (size_t)b * a.H + h;
+    const size_t st_off = (bh * a.S + s) * D + c * 8;     // [B,H,S,d]
+    const size_t ca_off = (bh * a.T + s) * D + c * 8;     // [B,H,T,d]
+    *reinterpret_cast<uint4 *>(a.qh + st_off) = pack8(q);
+    store_cache8(a, a.k_cache, ca_off, k);
+    store_cache8(a, a.v_cache, ca_off, v);
+    if (!a.cache_f16) {
+        *reinterpret_cast<uint4 *>(a.kh + st_off) = pack8(k);
+        *reinterpret_cast<uint4 *>(a.vh + st_off) = pack8(v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// attention
+// ------------------------------------------------------------------------------------------------
+struct __align__(8) PrefillBarriers {
+    uint64_t q_full;
+    uint64_t k_full[KV_STAGES], v_full[KV_STAGES], kv_empty[KV_STAGES];
+    uint64_t s_full[2], s_empty[2];
+    uint64_t p_full, p_empty, o_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int BN> struct PrefillCfg {
+    static constexpr int K_TILE_BYTES = BN * D * 2;     // K or V tile: BN keys x 128 dims fp16
+    static constexpr int K_HALF = K_TILE_BYTES / 2;     // one [BN x 64] swizzled block
+    static constexpr int P_BYTES = BM * BN * 2;         // P tile: BN/64 blocks of [128 x 64]
+    static constexpr uint32_t TMEM_COLS = (BN == 64) ? 256u : 512u; // S0, S1 (BN columns each) + O (128)
+    static constexpr size_t SMEM = (size_t)Q_TILE_BYTES + 2 * KV_STAGES * K_TILE_BYTES + P_BYTES + 256;
+};
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait (0.2 s of wall clock).  On failure raises the CTA's abort flag and the status bit.
+__device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, PrefillBarriers *pb, unsigned *status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = 1;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 0) {
+            if (*reinterpret_cast<volatile int *>(&pb->abort_flag)) return false;
+            if (globaltimer_ns() - t0 > 200000000ull) break;
+        }
+    }
+    *reinterpret_cast<volatile int *>(&pb->abort_flag) = 1;
+    atomicOr(status, kErrPrefillWait);
+    return false;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
+    flb_prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                            const __grid_constant__ CUtensorMap tmV, const PrefillArgs a) {
+    using Cfg = PrefillCfg<BN>;
+    constexpr int NCH = BN / 32; // 32-column chunks of one score row
+    // The 128-byte swizzle pattern is a function of address bits [4,10): tiles must start on 1 KB.
+    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char *sQ = smem;                                     // two [128 x 64] blocks
+    unsigned char *sK = sQ + Q_TILE_BYTES;                        // KV_STAGES tiles
+    unsigned char *sV = sK + KV_STAGES * Cfg::K_TILE_BYTES;       // KV_STAGES tiles
+    unsigned char *sP = sV + KV_STAGES * Cfg::K_TILE_BYTES;       // P
+    PrefillBarriers *pb = reinterpret_cast<PrefillBarriers *>(sP + Cfg::P_BYTES);
+    if (smem_u32(smem) & 1023u) { // never observed; without it the MMAs would read scrambled tiles
+        if (threadIdx.x == 0) atomicOr(a.status, kErrPrefillAlign);
+        return;
+    }
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nq = (a.S + BM - 1) / BM;
+    const int bh = blockIdx.x / nq;
+    const int qt = nq - 1 - (int)(blockIdx.x % nq); // heavy (late) query tiles first within a head
+    const int q0 = qt * BM;
+    const bool causal = (a.mask_mode == 2 || a.mask_mode == 3);
+    const int n_all = (a.S + BN - 1) / BN;
+    const int n_tiles = causal ? min(n_all, (q0 + BM) / BN) : n_all;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&pb->q_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(&pb->k_full[s], 1);
+            mbar_init(&pb->v_full[s], 1);
+            mbar_init(&pb->kv_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&pb->s_full[s], 1);
+            mbar_init(&pb->s_empty[s], 128);
+        }
+        mbar_init(&pb->p_full, 128);
+        mbar_init(&pb->p_empty, 1);
+        mbar_init(&pb->o_full, 1);
+        pb->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(&pb->tmem_base, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&pb->tmem_base);
+    const uint32_t tS[2] = {tmem, tmem + (uint32_t)BN};
+    const uint32_t tO = tmem + 2u * BN;
+
+    if (warp == 0) {
+        // ======================= TMA producer =======================
+        if (lane == 0) {
+            tma_prefetch_desc(&tmQ);
+            tma_prefetch_desc(&tmK);
+            tma_prefetch_desc(&tmV);
+            mbar_arrive_expect_tx(&pb->q_full, Q_TILE_BYTES);
+            tma_load_3d(sQ, &tmQ, 0, q0, bh, &pb->q_full);
+            tma_load_3d(sQ + Q_TILE_BYTES / 2, &tmQ, 64, q0, bh, &pb->q_full);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                const uint32_t u = (uint32_t)(j >> 1);
+                if (!wait_bar(&pb->kv_empty[s], (u & 1u) ^ 1u, pb, a.status)) break;
+                const int k0 = j * BN;
+                mbar_arrive_expect_tx(&pb->k_full[s], Cfg::K_TILE_BYTES);
+                tma_load_3d(sK + s * Cfg::K_TILE_BYTES, &tmK, 0, k0, bh, &pb->k_full[s]);
+                tma_load_3d(sK + s * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmK, 64, k0, bh, &pb->k_full[s]);
+                mbar_arrive_expect_tx(&pb->v_full[s], Cfg::K_TILE_BYTES);
+                tma_load_3d(sV + s * Cfg::K_TILE_BYTES, &tmV, 0, k0, bh, &pb->v_full[s]);
+                tma_load_3d(sV + s * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmV, 64, k0, bh, &pb->v_full[s]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ======================= MMA issuer =======================
+        if (lane == 0) {
+            // S = Q.K^T : A (Q) and B (K) both K-major, 128-byte swizzle, 8-row groups 1024 B apart
+            constexpr uint32_t idesc_qk = umma_idesc_f16(BM, BN, false, false);
+            // O += P.V  : A (P) K-major; B (V) MN-major: 64-dim blocks K_HALF apart (LBO), 8-key groups
+            // 1024 B apart (SBO)
+            constexpr uint32_t idesc_pv = umma_idesc_f16(BM, D, false, true);
+            const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
+            bool ok = wait_bar(&pb->q_full, 0, pb, a.status);
+
+            auto issue_pv = [&](int i) -> bool {
+                const int s = i & 1;
+                const uint32_t u = (uint32_t)(i >> 1);
+                if (!wait_bar(&pb->v_full[s], u & 1u, pb, a.status)) return false;
+                if (!wait_bar(&pb->p_full, (uint32_t)(i & 1), pb, a.status)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint64_t da = umma_desc_sw128(aP + (kk >> 2) * (BM * 128) + (kk & 3) * 32, 16, 1024);
+                    const uint64_t db = umma_desc_sw128(aV + s * Cfg::K_TILE_BYTES + kk * 2048, Cfg::K_HALF, 1024);
+                    umma_f16_ss(tO, da, db, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(&pb->kv_empty[s]);
+                umma_commit(&pb->p_empty);
+                return true;
+            };
+
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                const uint32_t u = (uint32_t)(j >> 1);
+                if (!wait_bar(&pb->k_full[s], u & 1u, pb, a.status)) { ok = false; break; }
+                if (!wait_bar(&pb->s_empty[s], (u & 1u) ^ 1u, pb, a.status)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint64_t da = umma_desc_sw128(aQ + (kk >> 2) * (Q_TILE_BYTES / 2) + (kk & 3) * 32, 16, 1024);
+                    const uint64_t db = umma_desc_sw128(aK + s * Cfg::K_TILE_BYTES + (kk >> 2) * Cfg::K_HALF + (kk & 3) * 32, 16, 1024);
+                    umma_f16_ss(tS[s], da, db, idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&pb->s_full[s]);
+                if (j >= 1) ok = issue_pv(j - 1);
+            }
+            if (ok) ok = issue_pv(n_tiles - 1);
+            if (ok) umma_commit(&pb->o_full);
+        }
+        __syncwarp();
+    } else {
+        // ======================= softmax / correction / epilogue =======================
+        const int quarter = warp & 3;                  // TMEM lane quarter this warp may access
+        const int lrow = quarter * 32 + lane;          // query row inside the tile
+        const int row = q0 + lrow;                     // query position
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const bool row_valid = row < a.S;
+        float m_used = -1e30f, l_sum = 0.f;
+        uint32_t r[NCH][32];
+        bool ok = true;
+
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1;
+            const uint32_t u = (uint32_t)(j >> 1);
+            const int k0 = j * BN;
+            ok = wait_bar(&pb->s_full[s], u & 1u, pb, a.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            // the whole score row of this tile into registers, then hand the S buffer back
+#pragma unroll
+            for (int ch = 0; ch < NCH; ++ch) tmem_ld32(tS[s] + lane_addr + ch * 32, r[ch]);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&pb->s_empty[s]);
+
+            const bool check = (causal && k0 + BN - 1 > q0) || (k0 + BN > a.S) || (a.mask_mode == 1);
+            float m_tile = -INFINITY;
+            if (!check) {
+                // fast path: every key of the tile is visible; scale > 0 commutes with max
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(r[ch][i]));
+                m_tile *= a.scale_log2e;
+            } else {
+                // keys this row may see inside the tile: [0, lim); scores become scaled (+ mask) in place
+                int lim = min(BN, a.S - k0);
+                if (a.mask_mode == 2) lim = min(lim, row - k0 + 1);
+                if (a.mask_mode == 3) lim = min(lim, row - k0);
+                const float *mrow = (a.mask_mode == 1 && row_valid) ? a.attn_mask + (size_t)row * a.mask_row_stride + k0 : nullptr;
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int c = ch * 32 + i;
+                        float x = __uint_as_float(r[ch][i]) * a.scale_log2e;
+                        if (mrow && c < lim) x += __ldg(mrow + c) * kLog2e;
+                        if (c >= lim) x = -INFINITY;
+                        r[ch][i] = __float_as_uint(x);
+                        m_tile = fmaxf(m_tile, x);
+                    }
+            }
+            // ---- the P buffer and O are free once P.V of the previous tile has completed
+            ok = wait_bar(&pb->p_empty, (uint32_t)((j & 1) ^ 1), pb, a.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            if (j == 0) {
+                m_used = fmaxf(m_tile, -1e30f);
+            } else {
+                const bool grow = m_tile > m_used + kRescaleThreshold;
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float m_new = fmaxf(m_used, m_tile);
+                    const float alpha = ex2(m_used - m_new);
+                    m_used = m_new;
+                    l_sum *= alpha;
+                    uint32_t o[32];
+#pragma unroll 1
+                    for (int ch = 0; ch < 4; ++ch) {
+                        tmem_ld32(tO + lane_addr + ch * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tO + lane_addr + ch * 32, o);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            // ---- P = exp2(x - m), row sum, fp16 P into the swizzled A-operand tile:
+            // element (lrow, c): block c/64, row lrow (128 B), 16-byte chunk ((c%64)/8) ^ (lrow%8)
+            const float sc = check ? 1.0f : a.scale_log2e; // slow path scaled the scores already
+            const float neg_m = -m_used;
+#pragma unroll
+            for (int ch = 0; ch < NCH; ++ch) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = ex2(fmaf(__uint_as_float(r[ch][i]), sc, neg_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(r[ch][i + 1]), sc, neg_m));
+                    l_sum += p0 + p1;
+                    const __half2 h2 = __floats2half2_rn(p0, p1);
+                    packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&h2);
+                }
+                unsigned char *blk = sP + (ch >> 1) * (BM * 128) + lrow * 128;
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int chunk = ((ch & 1) * 4 + t) ^ (lrow & 7);
+                    *reinterpret_cast<uint4 *>(blk + chunk * 16) =
+                        make_uint4(packed[4 * t], packed[4 * t + 1], packed[4 * t + 2], packed[4 * t + 3]);
+                }
+            }
+            // P (shared memory, generic proxy) and O (TMEM) ready for the tensor core
+            tc_fence_before();
+            fence_proxy_async_smem();
+            mbar_arrive(&pb->p_full);
+        }
+
+        // ---- epilogue: O / l
+        if (ok) {
+            ok = wait_bar(&pb->o_full, 0, pb, a.status);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv = (l_sum > 0.f) ? 1.0f / l_sum : 0.f; // fully masked row -> zeros
+            const size_t obase = ((size_t)bh * a.S + row) * D;
+            uint32_t o[32];
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                tmem_ld32(tO + lane_addr + ch * 32, o);
+                tmem_wait_ld();
+                if (row_valid) {
+                    if (a.out_f16) {
+                        uint4 *dst = reinterpret_cast<uint4 *>((__half *)a.out + obase + ch * 32);
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const __half2 h2 = __floats2half2_rn(__uint_as_float(o[8 * t + 2 * e]) * inv,
+                                                                     __uint_as_float(o[8 * t + 2 * e + 1]) * inv);
+                                w[e] = *reinterpret_cast<const uint32_t *>(&h2);
+                            }
+                            dst[t] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+                        float4 *dst = reinterpret_cast<float4 *>((float *)a.out + obase + ch * 32);
+#pragma unroll
+                        for (int t = 0; t < 8; ++t)
+                            dst[t] = make_float4(__uint_as_float(o[4 * t]) * inv, __uint_as_float(o[4 * t + 1]) * inv,
+                                                 __uint_as_float(o[4 * t + 2]) * inv, __uint_as_float(o[4 * t + 3]) * inv);
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, Cfg::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess) return nullptr;
+    if (qres != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(fn);
+}
+
+// fp16 tensor [bh][rows_valid of rows_stride][128], box = 64 dims x box_rows rows, 128-byte swizzle;
+// rows at or beyond rows_valid read as zeros.
+bool make_map(EncodeTiledFn enc, CUtensorMap *tm, const void *base, int BH, int rows_valid, int rows_stride, int box_rows) {
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows_valid, (cuuint64_t)BH};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)rows_stride * D * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+} // namespace
+
+int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
+    if (p->freq_cis && (reinterpret_cast<uintptr_t>(p->freq_cis) & 15u)) return FLB_ERR_MISALIGNED;
+    if (p->input_mode == FLB_IN_INT32 &&
+        ((reinterpret_cast<uintptr_t>(p->q_w_scale) | reinterpret_cast<uintptr_t>(p->k_w_scale) |
+          reinterpret_cast<uintptr_t>(p->v_w_scale)) & 15u))
+        return FLB_ERR_MISALIGNED;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return FLB_ERR_DEVICE;
+
+    const int B = p->batch_size, H = p->head_num, S = p->seq_len, T = p->total_len;
+    const size_t one = ((size_t)B * H * S * D * 2 + 255) / 256 * 256;
+    unsigned char *sc = static_cast<unsigned char *>(p->scratch);
+
+    PrefillArgs a;
+    a.B = B; a.H = H; a.S = S; a.T = T;
+    a.input_mode = p->input_mode;
+    a.q = p->q; a.k = p->k; a.v = p->v;
+    a.act_scale = p->act_scale; a.q_w_scale = p->q_w_scale; a.k_w_scale = p->k_w_scale; a.v_w_scale = p->v_w_scale;
+    a.freq_cis = p->freq_cis;
+    a.rope_pos0 = p->rope_pos0;
+    a.k_cache = p->k_cache; a.v_cache = p->v_cache;
+    a.cache_f16 = (p->cache_dtype == FLB_F16);
+    a.qh = reinterpret_cast<__half *>(sc + 256);
+    a.kh = reinterpret_cast<__half *>(sc + 256 + one);
+    a.vh = reinterpret_cast<__half *>(sc + 256 + 2 * one);
+    a.mask_mode = p->mask_mode;
+    a.attn_mask = p->attn_mask;
+    a.mask_row_stride = p->mask_row_stride;
+    a.out = p->out;
+    a.out_f16 = (p->out_dtype == FLB_F16);
+    a.scale_log2e = p->softmax_scale * kLog2e;
+    a.status = reinterpret_cast<unsigned *>(sc);
+
+    CUtensorMap tmQ, tmK, tmV;
+    constexpr int BN = kKeysPerTile;
+    bool ok = make_map(enc, &tmQ, a.qh, B * H, S, S, BM);
+    if (a.cache_f16) {
+        ok = ok && make_map(enc, &tmK, p->k_cache, B * H, S, T, BN) && make_map(enc, &tmV, p->v_cache, B * H, S, T, BN);
+    } else {
+        ok = ok && make_map(enc, &tmK, a.kh, B * H, S, S, BN) && make_map(enc, &tmV, a.vh, B * H, S, S, BN);
+    }
+    if (!ok) return FLB_ERR_LAUNCH;
+
+    if (cudaMemsetAsync(sc, 0, 256, stream) != cudaSuccess) return FLB_ERR_LAUNCH;
+    const size_t total = (size_t)B * S * H * 16;
+    flb_prefill_prologue_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a);
+    if (cudaGetLastError() != cudaSuccess) return FLB_ERR_LAUNCH;
+
+    static_assert(sizeof(PrefillBarriers) <= 256, "barrier block must fit its slot");
+    constexpr size_t smem = PrefillCfg<BN>::SMEM;
+    if (cudaFuncSetAttribute(flb_prefill_attn_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return FLB_ERR_LAUNCH;
+    const int nq = (S + BM - 1) / BM;
+    flb_prefill_attn_kernel<BN><<<(unsigned)(B * H * nq), NUM_THREADS, smem, stream>>>(tmQ, tmK, tmV, a);
+    if (cudaGetLastError() != cudaSuccess) return FLB_ERR_LAUNCH;
+    return FLB_OK;
+}
+
 } // namespace flb

@@ -138,9 +138,15 @@ void orc_softmax_row(float *qk, const float *mask_row, int n, float scaler, int 
 // prefill (S > 1) attends over the fresh rows only, like the reference, and needs past == 0.
 // With an fp16 cache the appended rows are rounded to half first and the rounded values are the
 // ones attended over, so that this step and later steps see the same K/V.
-// `acc_double` != 0 accumulates the two contractions in double (the arbiter); 0 uses fp32 FMA-free
-// left-to-right sums.  Returns 0, or a negative flb_status.
-int orc_attention(const flb_attn_params *p, int acc_double) {
+// `flags` bit 0: accumulate the two contractions in double (the arbiter); clear = fp32 left-to-right
+// sums.  Bit 1: round the prefill operands q, k, v to fp16 before the contractions — the
+// reference's prefill GEMMs run fp16 tensor-core math on fp32 storage (CUBLAS_COMPUTE_32F_FAST_16F,
+// fasterLlama/cuda/common.h:71), so this is the operand precision of its own prefill; decode
+// (cublasSgemv, true fp32) ignores the bit.  The cache always receives the unrounded values.
+// Returns 0, or a negative flb_status.
+int orc_attention(const flb_attn_params *p, int flags) {
+    const int acc_double = flags & 1;
+    const bool f16_operands = (flags & 2) != 0 && p->seq_len > 1;
     const int B = p->batch_size, H = p->head_num, d = p->size_per_head, S = p->seq_len, T = p->total_len;
     if (B <= 0 || H <= 0 || d <= 0 || (d & 1) || S <= 0 || T <= 0) return FLB_ERR_BAD_SHAPE;
     if (!p->q || !p->k || !p->v || !p->k_cache || !p->v_cache || !p->out) return FLB_ERR_NULL_POINTER;
@@ -194,12 +200,16 @@ int orc_attention(const flb_attn_params *p, int acc_double) {
             // exactly the fresh rows).
             auto Kat = [&](int r, int i) -> float {
                 const size_t c = slab + (size_t)r * d + i;
-                return cache16 ? HalfBits::to_float(((const uint16_t *)p->k_cache)[c]) : ((const float *)p->k_cache)[c];
+                const float x = cache16 ? HalfBits::to_float(((const uint16_t *)p->k_cache)[c]) : ((const float *)p->k_cache)[c];
+                return f16_operands ? half_round(x) : x;
             };
             auto Vat = [&](int r, int i) -> float {
                 const size_t c = slab + (size_t)r * d + i;
-                return cache16 ? HalfBits::to_float(((const uint16_t *)p->v_cache)[c]) : ((const float *)p->v_cache)[c];
+                const float x = cache16 ? HalfBits::to_float(((const uint16_t *)p->v_cache)[c]) : ((const float *)p->v_cache)[c];
+                return f16_operands ? half_round(x) : x;
             };
+            if (f16_operands)
+                for (size_t i = 0; i < qv.size(); ++i) qv[i] = half_round(qv[i]);
             std::vector<float> sc(L), mrow(L);
             for (int s = 0; s < S; ++s) {
                 const int qpos = past + s;

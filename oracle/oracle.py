@@ -39,10 +39,12 @@ def load():
     return _lib
 
 
-def attention(params, acc_double: bool = True) -> None:
+def attention(params, acc_double: bool = True, f16_operands: bool = False) -> None:
     """Runs the whole path on the host.  `params` is a flb_attn_params block whose pointers are
-    HOST memory (numpy arrays); the caches and `out` arrays are written in place."""
-    st = load().orc_attention(C.addressof(params), int(acc_double))
+    HOST memory (numpy arrays); the caches and `out` arrays are written in place.
+    `f16_operands` rounds the prefill operands to fp16 first (the precision of the reference's
+    own fp16 tensor-core prefill GEMMs); decode ignores it."""
+    st = load().orc_attention(C.addressof(params), int(acc_double) | (2 if f16_operands else 0))
     if st != 0:
         raise RuntimeError(f"oracle rejected the parameters: status {st}")
 

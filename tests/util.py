@@ -38,13 +38,13 @@ def assert_abs_close(got: np.ndarray, want: np.ndarray, tol: float = FP16_ABS, w
         raise AssertionError(f"{what}: max abs err {err.max():.3e} > {tol:g} at {i}: got {got[i]!r} want {want[i]!r}")
 
 
-def run_oracle(case: W.Case) -> dict[str, np.ndarray]:
+def run_oracle(case: W.Case, f16_operands: bool = False) -> dict[str, np.ndarray]:
     """Runs the host oracle on copies of the case's arrays; returns out and the updated caches."""
     from oracle import oracle
 
     arrays = {k: np.array(v, copy=True) for k, v in case.arrays.items()}
     p = case.params(arrays)
-    oracle.attention(p, acc_double=True)
+    oracle.attention(p, acc_double=True, f16_operands=f16_operands)
     return {"out": arrays["out"], "k_cache": arrays["k_cache"], "v_cache": arrays["v_cache"]}
 
 
