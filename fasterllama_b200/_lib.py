@@ -80,6 +80,7 @@ EXPORTS = {
     "flb_attn_forward": (C.c_int, [_PP, C.c_void_p]),
     "flb_attn_classify_mask": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_int), C.c_void_p]),
     "flb_attn_scratch_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint), C.c_void_p]),
+    "flb_attn_decode_static_scratch": (C.c_int, [_PP, C.c_void_p]),
 }
 
 _lib = None

@@ -160,6 +160,12 @@ def decode(p: FlbAttnParams, stream=None) -> None:
     _lib.check(_lib.load_library().flb_attn_decode(C.byref(p), _stream_handle(stream)))
 
 
+def decode_static_scratch(p: FlbAttnParams, stream=None) -> None:
+    """Decode with the library's own fixed scratch block (for callers that cannot provide any):
+    `p.scratch` is ignored.  One block per GPU — keep these calls on one stream."""
+    _lib.check(_lib.load_library().flb_attn_decode_static_scratch(C.byref(p), _stream_handle(stream)))
+
+
 def prefill(p: FlbAttnParams, stream=None) -> None:
     _lib.check(_lib.load_library().flb_attn_prefill(C.byref(p), _stream_handle(stream)))
 

@@ -183,6 +183,25 @@ int flb_attn_classify_mask(const float *attn_mask, int rows, int row_stride, voi
  * stream.  The reference has no counterpart: its kernels cannot report anything. */
 int flb_attn_scratch_status(const void *scratch, unsigned *status_out, void *cuda_stream);
 
+/* Bytes of device memory the library itself holds, on every GPU that loads it, for
+ * flb_attn_decode_static_scratch(). */
+#define FLB_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+
+/* Decode for callers that have no scratch to give: same work as flb_attn_decode(), but the
+ * split-KV scratch is a fixed FLB_STATIC_SCRATCH_BYTES block built into the library, so the call
+ * needs nothing beyond the caller's inputs and outputs and never allocates.  The fields scratch,
+ * scratch_bytes and scratch_zeroed of `p` are ignored.  This entry point has no counterpart in the
+ * reference (whose OpenDecoder is always handed a workspace by its caller).
+ *   - Limit: batch_size * head_num * partitions-per-sequence must fit the block (about 520 bytes
+ *     per partition: 16 MiB holds e.g. batch 64 x 40 heads x 8 partitions).  Larger calls return
+ *     FLB_ERR_TOO_LARGE and launch nothing.
+ *   - The first call on each GPU looks the block's address up (not a stream operation): make that
+ *     call before starting any stream capture on that GPU.
+ *   - One block per GPU, shared by every call: calls that may overlap on a GPU race with each
+ *     other; keep them on one stream.  The status word read by flb_attn_scratch_status() lives in
+ *     the block and is not reachable through this entry point. */
+int flb_attn_decode_static_scratch(const flb_attn_params *p, void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
