@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the decode-attention hot path (one JSON line on stdout, rank 0).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c4|c3]
 
 A step is one decode-attention call (one new token per sequence, one decoder layer) over one batch
 of synthetic input: by default fp16, batch 16, 32 heads x 128, cached lengths uniform in
@@ -17,6 +17,9 @@ data path: weak scaling) and the value is the sum over ranks divided by the slow
 `roofline` the decode kernel's bytes per launch over its average duration (CUDA events on the
           launching stream), against the measured copy bandwidth of this pool's B200s.
 `cpu_baseline` the scalar host oracle timed on this box's cores on a bounded sample.
+
+`--workload c4` is the 13B-shape batch split over the ranks (strong scaling); `--workload c3` is the
+causal prefill (metric TFLOP/s of causal-exact flops, tensor roofline).
 
 `--impl reference` times the reference's own CUDA attention chain (three kernels + two cuBLAS gemv
 + softmax, fp32 cache) built from the reference checkout by oracle/build_ref.sh; the reference has
@@ -47,6 +50,7 @@ WORKLOADS = {
     "c2": (16, 32, 1024, 2048, 1, "fp16 decode attention, LLaMA-2-7B layer shape: batch 16, 32 heads x 128, cached lengths U[1024,2048], seed 1"),
     "c4": (64, 40, 2048, 4096, 3, "fp16 decode attention, LLaMA-2-13B layer shape: batch 64, 40 heads x 128, cached lengths U[2048,4096], seed 3"),
 }
+PREFILL_WORKLOADS = ("c3",)
 
 
 def load_peaks() -> tuple[float, str]:
@@ -173,18 +177,27 @@ def run_ours(args, rank, world, local):
     from fasterllama_b200 import attention as A
     from fasterllama_b200 import workloads as W
 
+    from fasterllama_b200 import sharding
+
     global NBUF
     NBUF = max(1, args.sets)
     B, H, lo, hi, seed, desc = WORKLOADS[args.workload]
     T = hi + 1
     dev = f"cuda:{local}"
     lens = W.draw_lengths(seed, B, lo, hi)  # the same lengths on every rank and in every set
+    strong = args.workload == "c4"  # config 4 is quoted as one batch sharded over the GPUs
+    if strong:
+        sh = sharding.plan(B, H, world, rank)
+        if sh.axis == "batch":
+            lens = lens[sh.start:sh.stop]
+        B, H = sh.batch, sh.heads
     sets = []
     for j in range(NBUF):
         c = W.device_case(f"{args.workload}-{j}", seed + 7919 * j + 104729 * rank, B, H, T, lens, device=dev)
         c.scratch_zeroed = True  # device_case hands over zeroed scratch; the kernel leaves it zeroed
         sets.append((c, c.params()))
     bytes_step = sets[0][0].algorithmic_bytes()
+    tokens_step = WORKLOADS[args.workload][0] if strong else B * world  # sequences advanced per step, all ranks
     stream = torch.cuda.current_stream()
 
     def step(i):
@@ -244,19 +257,20 @@ def run_ours(args, rank, world, local):
     line = {
         "metric": "decode_attn_hbm_gbps", "value": round(value, 1), "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": round(t / args.steps * 1e3, 5), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(t / args.steps * 1e3, 5), "higher_is_better": True, "scaling": "strong" if strong else "weak",
         "vs_baseline": None, "dtype": "f16 storage, f32 arithmetic", "data": "synthetic",
         "config": {
             "workload": desc, "per_gpu_batch": B, "heads": H, "head_dim": 128, "cache_rows_total": int(lens.sum()),
             "total_len": T, "split_len": 512, "l2": f"{NBUF} distinct input sets rotated ({NBUF * bytes_step / 1e6:.0f} MB > 126 MB L2), no flush kernel in the timed region",
-            "sharding": "independent (batch, head) units per rank, no collective",
+            "sharding": ("one batch split over the ranks by contiguous (batch, head) ranges, no collective" if strong
+                         else "every rank runs its own batch of this shape (independent (batch, head) units), no collective"),
         },
-        "tokens_per_s": round(B * world * args.steps / t, 1),
+        "tokens_per_s": round(tokens_step * args.steps / t, 1),
         "pct_of_8TBps": round(100 * value / world / 8000.0, 2),
         "bytes_per_step_per_gpu": bytes_step,
         "gpu_launches": args.steps,
         "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": round(t_e2e / args.steps * 1e3, 5), "tokens_per_s": round(B * world * args.steps / t_e2e, 1)},
+                "ms_per_step": round(t_e2e / args.steps * 1e3, 5), "tokens_per_s": round(tokens_step * args.steps / t_e2e, 1)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "peak_source": f"{peak_src} (copy bandwidth, MEASURED_PEAKS.json)",
                      "kernel": "flb_decode_attn_kernel<__half,...>", "traffic": DRAM_TRAFFIC_PER_LAUNCH.get(args.workload)},
@@ -264,6 +278,101 @@ def run_ours(args, rank, world, local):
     }
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(sets[0][0], bytes_step, B)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def run_prefill(args, rank, world, local):
+    """Config 3: fp16 causal prefill, batch 8, 1024 tokens, 32 heads x 128, seed 2 (every rank its own
+    batch).  A step = prologue (dequant/RoPE/transpose/cache append) + tensor-core attention."""
+    from fasterllama_b200 import attention as A
+    from fasterllama_b200 import workloads as W
+
+    B, H, S = 8, 32, 1024
+    dev = f"cuda:{local}"
+    g = torch.Generator(device=dev)
+    g.manual_seed(2 + rank)
+    nbuf = max(1, min(args.sets, 2))
+    sets = []
+    for j in range(nbuf):
+        a = {n: torch.randn((B, S, H, 128), generator=g, device=dev).to(torch.float16) for n in ("q", "k", "v")}
+        a["k_cache"] = torch.zeros((B, H, S, 128), device=dev, dtype=torch.float16)
+        a["v_cache"] = torch.zeros_like(a["k_cache"])
+        a["out"] = torch.zeros((B, H, S, 128), device=dev, dtype=torch.float16)
+        a["freq_cis"] = torch.from_numpy(W.freq_cis_table(S)).to(dev)
+        a["scratch"] = torch.zeros(A.workspace_bytes(B, H, S, S), dtype=torch.uint8, device=dev)
+        c = W.Case(name="c3", B=B, H=H, S=S, T=S, start_pos=0, arrays=a, rope_add_past=True)
+        sets.append((c, c.params()))
+    stream = torch.cuda.current_stream()
+    flops = B * H * 2 * 128 * S * (S + 1)  # causal-exact: two contractions over the visible pairs
+
+    def step(i):
+        A.prefill(sets[i % nbuf][1], stream)
+
+    steps = min(args.steps, 500)
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    sampler.start()
+    e0.record(stream)
+    for i in range(steps):
+        step(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    sampler.stop()
+    t_dev = e0.elapsed_time(e1) * 1e-3
+    t = max_over_ranks(t_dev, world)
+    for c, _ in sets:
+        assert A.scratch_status(c.arrays["scratch"]) == 0, "a prefill kernel reported an error status"
+
+    host_in = [{n: c.arrays[n].cpu().pin_memory() for n in ("q", "k", "v")} for c, _ in sets]
+    host_out = torch.empty_like(sets[0][0].arrays["out"], device="cpu").pin_memory()
+    h2d = sum(v.numel() * v.element_size() for v in host_in[0].values())
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step(i):
+        c, p = sets[i % nbuf]
+        for n in ("q", "k", "v"):
+            c.arrays[n].copy_(host_in[i % nbuf][n], non_blocking=True)
+        A.prefill(p, stream)
+        host_out.copy_(c.arrays["out"], non_blocking=True)
+        stream.synchronize()
+
+    e2e_steps = min(steps, 50)
+    for i in range(2):
+        e2e_step(i)
+    barrier(world)
+    e0.record(stream)
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t_e2e = max_over_ranks(e0.elapsed_time(e1) * 1e-3, world)
+    barrier(world)
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+        peak_src = "measured (cuBLAS bf16 burst, MEASURED_PEAKS.json)"
+    except Exception:
+        peak, peak_src = 1590.0, "fallback"
+    value = flops * world * steps / t / 1e12
+    achieved = flops * steps / t_dev / 1e12
+    line = {
+        "metric": "prefill_attn_tflops", "value": round(value, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(t / steps * 1e3, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 operands, f32 accumulation", "data": "synthetic",
+        "config": {"workload": "fp16 causal prefill attention, LLaMA-2-7B layer shape: batch 8, 1024 tokens, 32 heads x 128, RoPE rows 0..1023, seed 2",
+                   "flops_per_step": flops, "l2": f"{nbuf} distinct input sets rotated; q/k/v/caches of one set = 0.4 GB > 126 MB L2"},
+        "tokens_per_s": round(B * S * world * steps / t, 1),
+        "gpu_launches": 2 * steps,
+        "e2e": {"value": round(flops * world * e2e_steps / t_e2e / 1e12, 1), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(t_e2e / e2e_steps * 1e3, 5)},
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
+                     "frac": round(achieved / peak, 4), "peak_source": peak_src,
+                     "kernel": "flb_prefill_prologue_kernel + flb_prefill_attn_kernel<64> (whole step)", "traffic": None},
+        "clocks": sampler.summary(),
+    }
     if rank == 0:
         print(json.dumps(line), flush=True)
 
@@ -317,6 +426,8 @@ def run_reference(args, rank, world, local):
         return
     from fasterllama_b200 import workloads as W
 
+    if args.workload in PREFILL_WORKLOADS:
+        return run_reference_prefill(args, local)
     B, H, lo, hi, seed, desc = WORKLOADS[args.workload]
     T, d = hi + 1, 128
     dev = f"cuda:{local}"
@@ -411,13 +522,61 @@ def run_reference(args, rank, world, local):
     ref.close()
 
 
+def run_reference_prefill(args, local):
+    """The reference's prefill chain (3 kernels, 2 batched cuBLAS GEMMs with fp16 tensor-core math on
+    fp32 storage, softmax over the materialised 1 GiB score matrix) at the config-3 shape."""
+    from fasterllama_b200 import workloads as W
+    from oracle import ref_runner
+
+    B, H, S, d = 8, 32, 1024, 128
+    dev = f"cuda:{local}"
+    ref = ref_runner.RefRunner()
+    g = torch.Generator(device=dev)
+    g.manual_seed(2)
+    t = {n: torch.randint(-8192, 8192, (B, S, H, d), generator=g, device=dev, dtype=torch.int32) for n in ("q", "k", "v")}
+    t.update(act_scale=torch.full((B * S,), 2.0**-7, device=dev), q_w_scale=torch.full((H * d,), 2.0**-6, device=dev),
+             k_w_scale=torch.full((H * d,), 2.0**-6, device=dev), v_w_scale=torch.full((H * d,), 2.0**-6, device=dev),
+             freq_cis=ref.freq_cis(S + 8), attn_mask=torch.from_numpy(W.causal_mask(S, strict=False)).to(dev),
+             k_cache=torch.zeros((B, H, S, d), device=dev), v_cache=torch.zeros((B, H, S, d), device=dev),
+             out=torch.zeros((B, H, S, d), device=dev))
+    a = ref.make_args(t, start_pos=0)
+    stream = torch.cuda.current_stream()
+    steps = min(args.steps, 100)
+    for _ in range(3):
+        assert ref.attention(a, stream.cuda_stream) == 0
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    sampler.start()
+    e0.record(stream)
+    for _ in range(steps):
+        ref.attention(a, stream.cuda_stream)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    sampler.stop()
+    tt = e0.elapsed_time(e1) * 1e-3
+    flops = B * H * 2 * d * S * (S + 1)
+    v = flops * steps / tt / 1e12
+    line = {"impl": "reference", "metric": "prefill_attn_tflops", "value": round(v, 1), "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": steps, "warmup": 3, "ms_per_step": round(tt / steps * 1e3, 5), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 storage, fp16 tensor-core math (CUBLAS_COMPUTE_32F_FAST_16F)", "data": "synthetic",
+            "config": {"workload": "causal prefill attention, batch 8, 1024 tokens, 32 heads x 128", "flop_basis": "causal-exact flops, identical to the other arm (the reference computes the full square)"},
+            "gpu_launches": steps * 6,
+            "cpu_baseline": {"value": round(v, 1), "unit": "TFLOP/s", "cores": 0, "kind": "reference",
+                             "sample": "the whole batch; the reference has no CPU implementation of this path, so its own CUDA kernels run on the GPU"},
+            "e2e": {"value": round(v, 1), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "clocks": sampler.summary()}
+    print(json.dumps(line), flush=True)
+    ref.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + list(PREFILL_WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the host-oracle baseline leg")
     ap.add_argument("--sets", type=int, default=NBUF, help="distinct input sets rotated through the loop (1 for a small profiler capture)")
     args = ap.parse_args()
@@ -438,7 +597,10 @@ def main():
             from fasterllama_b200 import _lib
 
             _lib.load_library()  # no fallback: fail here if the CUDA library is missing
-            run_ours(args, rank, world, local)
+            if args.workload in PREFILL_WORKLOADS:
+                run_prefill(args, rank, world, local)
+            else:
+                run_ours(args, rank, world, local)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -1,0 +1,83 @@
+"""Multi-rank host logic on CPU: two gloo ranks each take their shard of a decode batch, run it (the
+host oracle stands in for the device), gather, and must reproduce the unsharded result exactly."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from fasterllama_b200 import sharding
+from fasterllama_b200 import workloads as W
+
+
+def test_plan_covers_every_unit_once():
+    for B, H, world in [(64, 40, 1), (64, 40, 2), (64, 40, 4), (64, 40, 8), (3, 32, 4), (16, 32, 8)]:
+        seen = np.zeros((B, H), dtype=int)
+        for r in range(world):
+            s = sharding.plan(B, H, world, r)
+            if s.axis == "batch":
+                seen[s.start:s.stop, :] += 1
+            else:
+                seen[:, s.start:s.stop] += 1
+            assert s.units * world == B * H
+        assert (seen == 1).all()
+    with pytest.raises(ValueError):
+        sharding.plan(3, 5, 2, 0)
+    with pytest.raises(ValueError):
+        sharding.plan(4, 4, 2, 2)
+
+
+def _contig(a):
+    return {k: (np.ascontiguousarray(v) if isinstance(v, np.ndarray) else v) for k, v in a.items()}
+
+
+def _worker(rank, world, port, axis_case, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from util import run_oracle
+
+        B, H = axis_case
+        lens = np.array([300, 5, 700, 64, 0, 513][:B], dtype=np.int32)
+        case = W.host_case("shard", 5, B, H, 800, past=lens, in_dtype="int32")
+        full = run_oracle(case)["out"]
+        sh = sharding.plan(B, H, world, rank)
+        part = W.Case(name="part", B=sh.batch, H=sh.heads, S=1, T=case.T, start_pos=0,
+                      arrays=_contig(sharding.slice_arrays(case.arrays, sh)), rope_add_past=True,
+                      mask_mode=case.mask_mode, max_past_len=case.max_past_len)
+        mine = torch.from_numpy(run_oracle(part)["out"])
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        cat = torch.cat(gathered, dim=0 if sh.axis == "batch" else 1).numpy()
+        # timing reduction used by the benchmark: max over ranks
+        t = torch.tensor([float(rank + 1)], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ok = np.array_equal(cat, full) and t.item() == world
+        if rank == 0:
+            ret.put((sh.axis, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("shape", [(4, 8), (3, 8)])  # batch divides / only heads divide
+def test_two_gloo_ranks_reproduce_the_unsharded_result(shape):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, shape, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    axis, ok = ret.get(timeout=10)
+    assert ok
+    assert axis == ("batch" if shape[0] % 2 == 0 else "head")
