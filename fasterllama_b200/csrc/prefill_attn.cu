@@ -37,9 +37,10 @@ namespace {
 
 constexpr int D = 128;       // head dimension
 constexpr int BM = 128;      // query rows per CTA
-constexpr int KV_STAGES = 2;
+constexpr int K_STAGES = 3;              // K ring: a stage is free again once S_j = Q.K_j^T has completed
+constexpr int V_STAGES = 2;              // V ring: a stage is free again once O += P_j.V_j has completed
 constexpr int Q_TILE_BYTES = BM * D * 2; // 128 x 128 fp16 = 32 KB, two [128 x 64] swizzled blocks
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 224;         // warps: 0 Q+K loads, 1 MMA, 2-5 softmax, 6 V loads
 constexpr int kKeysPerTile = 64;         // BN: 112 KB of shared memory and 256 TMEM columns per CTA -> 2 CTAs per SM
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f; // log2 domain: P stays below 2^8, exact in fp16 range
@@ -68,31 +69,40 @@ struct PrefillArgs {
 // ------------------------------------------------------------------------------------------------
 // prologue
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void load8(const PrefillArgs &a, const void *base, const float *w_scale, size_t off, int b_s, int h,
-                                      int c, float (&x)[8]) {
-    if (a.input_mode == 0) {
-        // float(acc) * act_scale * w_scale, in this order (decoder_kernels.cu:449, :875)
-        const int4 lo = __ldg(reinterpret_cast<const int4 *>((const int32_t *)base + off));
-        const int4 hi = __ldg(reinterpret_cast<const int4 *>((const int32_t *)base + off) + 1);
-        const float as = __ldg(a.act_scale + b_s);
-        const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w_scale + (size_t)h * D + c * 8));
-        const float4 w1 = __ldg(reinterpret_cast<const float4 *>(w_scale + (size_t)h * D + c * 8) + 1);
-        x[0] = (float)lo.x * as * w0.x;
-        x[1] = (float)lo.y * as * w0.y;
-        x[2] = (float)lo.z * as * w0.z;
-        x[3] = (float)lo.w * as * w0.w;
-        x[4] = (float)hi.x * as * w1.x;
-        x[5] = (float)hi.y * as * w1.y;
-        x[6] = (float)hi.z * as * w1.z;
-        x[7] = (float)hi.w * as * w1.w;
-    } else if (a.input_mode == 1) {
-        const float4 lo = __ldg(reinterpret_cast<const float4 *>((const float *)base + off));
-        const float4 hi = __ldg(reinterpret_cast<const float4 *>((const float *)base + off) + 1);
-        x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
-        x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+// Raw 8-element load (no use of the data: the conversion comes after every load of the thread has
+// been issued).  MODE: 0 = int32 accumulators, 1 = fp32, 2 = fp16.
+struct Raw8 {
+    uint4 lo, hi; // fp16 uses lo only
+};
+template <int MODE> __device__ __forceinline__ Raw8 load_raw8(const void *base, size_t off) {
+    Raw8 r;
+    if (MODE == 2) {
+        r.lo = __ldg(reinterpret_cast<const uint4 *>((const __half *)base + off));
+        r.hi = make_uint4(0, 0, 0, 0);
     } else {
-        const uint4 u = __ldg(reinterpret_cast<const uint4 *>((const __half *)base + off));
-        const __half2 *hp = reinterpret_cast<const __half2 *>(&u);
+        const uint4 *p = reinterpret_cast<const uint4 *>((const uint32_t *)base + off);
+        r.lo = __ldg(p);
+        r.hi = __ldg(p + 1);
+    }
+    return r;
+}
+template <int MODE>
+__device__ __forceinline__ void convert8(const Raw8 &r, float as, const float4 &w0, const float4 &w1, float (&x)[8]) {
+    if (MODE == 0) {
+        // float(acc) * act_scale * w_scale, in this order (decoder_kernels.cu:449, :875)
+        x[0] = (float)(int)r.lo.x * as * w0.x;
+        x[1] = (float)(int)r.lo.y * as * w0.y;
+        x[2] = (float)(int)r.lo.z * as * w0.z;
+        x[3] = (float)(int)r.lo.w * as * w0.w;
+        x[4] = (float)(int)r.hi.x * as * w1.x;
+        x[5] = (float)(int)r.hi.y * as * w1.y;
+        x[6] = (float)(int)r.hi.z * as * w1.z;
+        x[7] = (float)(int)r.hi.w * as * w1.w;
+    } else if (MODE == 1) {
+        x[0] = __uint_as_float(r.lo.x); x[1] = __uint_as_float(r.lo.y); x[2] = __uint_as_float(r.lo.z); x[3] = __uint_as_float(r.lo.w);
+        x[4] = __uint_as_float(r.hi.x); x[5] = __uint_as_float(r.hi.y); x[6] = __uint_as_float(r.hi.z); x[7] = __uint_as_float(r.hi.w);
+    } else {
+        const __half2 *hp = reinterpret_cast<const __half2 *>(&r.lo);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 t = __half22float2(hp[i]);
@@ -120,44 +130,84 @@ __device__ __forceinline__ void store_cache8(const PrefillArgs &a, void *cache, 
     }
 }
 
-// one thread per 8 consecutive head dimensions of one (b, s, h)
-__global__ void __launch_bounds__(256) flb_prefill_prologue_kernel(const PrefillArgs a) {
-    const size_t total = (size_t)a.B * a.S * a.H * 16;
-    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
-    if (idx >= total) return;
-    const int c = (int)(idx & 15);
-    const int h = (int)((idx >> 4) % a.H);
-    const int s = (int)((idx / (16 * (size_t)a.H)) % a.S);
-    const int b = (int)(idx / (16 * (size_t)a.H * a.S));
-    const size_t in_off = (((size_t)b * a.S + s) * a.H + h) * D + c * 8;
-    float q[8], k[8], v[8];
-    load8(a, a.q, a.q_w_scale, in_off, b * a.S + s, h, c, q);
-    load8(a, a.k, a.k_w_scale, in_off, b * a.S + s, h, c, k);
-    load8(a, a.v, a.v_w_scale, in_off, b * a.S + s, h, c, v);
-    if (a.freq_cis) {
-        // pairs (2i, 2i+1): x' = x cos - y sin ; y' = y cos + x sin (decoder_kernels.cu:455-458)
-        const float4 *fr = reinterpret_cast<const float4 *>(a.freq_cis + (size_t)(a.rope_pos0 + s) * D + c * 8);
-        const float4 f0 = __ldg(fr), f1 = __ldg(fr + 1);
-        const float cs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+// Each thread takes 8 consecutive head dimensions of kRowsPerThread tokens of one (b, h); a block of
+// 256 threads covers 16 * kRowsPerThread consecutive tokens: it reads 256-byte segments (token stride
+// H*d) and writes 4 KB runs into each of the [B,H,*,d] destinations.  All loads of a thread are
+// issued before the first use, so that enough bytes are in flight to cover the DRAM latency.
+constexpr int kRowsPerThread = 2;
+
+__device__ __forceinline__ void rope8(const float4 &f0, const float4 &f1, float (&x)[8]) {
+    // pairs (2i, 2i+1): x' = x cos - y sin ; y' = y cos + x sin (decoder_kernels.cu:455-458)
+    const float cs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-            const float co = cs[i], sn = cs[i + 1];
-            const float qx = q[i], qy = q[i + 1], kx = k[i], ky = k[i + 1];
-            q[i] = qx * co - qy * sn;
-            q[i + 1] = qy * co + qx * sn;
-            k[i] = kx * co - ky * sn;
-            k[i + 1] = ky * co + kx * sn;
+    for (int i = 0; i < 8; i += 2) {
+        const float co = cs[i], sn = cs[i + 1];
+        const float a0 = x[i], a1 = x[i + 1];
+        x[i] = a0 * co - a1 * sn;
+        x[i + 1] = a1 * co + a0 * sn;
+    }
+}
+
+template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_kernel(const PrefillArgs a) {
+    constexpr int R = kRowsPerThread;
+    const int sblocks = (a.S + 16 * R - 1) / (16 * R);
+    const int c = threadIdx.x & 15;
+    const int s0 = (int)(blockIdx.x % sblocks) * (16 * R) + (threadIdx.x >> 4);
+    const int h = (int)((blockIdx.x / sblocks) % a.H);
+    const int b = (int)(blockIdx.x / ((size_t)sblocks * a.H));
+    Raw8 rq[R], rk[R], rv[R];
+    float4 f0[R], f1[R];
+    float as[R];
+    // ---- every load first
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int s = min(s0 + 16 * r, a.S - 1); // rows past the end load a valid row and are not stored
+        const size_t in_off = (((size_t)b * a.S + s) * a.H + h) * D + c * 8;
+        rq[r] = load_raw8<MODE>(a.q, in_off);
+        rk[r] = load_raw8<MODE>(a.k, in_off);
+        rv[r] = load_raw8<MODE>(a.v, in_off);
+        as[r] = (MODE == 0) ? __ldg(a.act_scale + (size_t)b * a.S + s) : 1.0f;
+        if (a.freq_cis) {
+            const float4 *fr = reinterpret_cast<const float4 *>(a.freq_cis + (size_t)(a.rope_pos0 + s) * D + c * 8);
+            f0[r] = __ldg(fr);
+            f1[r] = __ldg(fr + 1);
         }
     }
+    float4 wq0, wq1, wk0, wk1, wv0, wv1;
+    wq0 = wq1 = wk0 = wk1 = wv0 = wv1 = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (MODE == 0) {
+        const size_t wo = (size_t)h * D + c * 8;
+        wq0 = __ldg(reinterpret_cast<const float4 *>(a.q_w_scale + wo));
+        wq1 = __ldg(reinterpret_cast<const float4 *>(a.q_w_scale + wo) + 1);
+        wk0 = __ldg(reinterpret_cast<const float4 *>(a.k_w_scale + wo));
+        wk1 = __ldg(reinterpret_cast<const float4 *>(a.k_w_scale + wo) + 1);
+        wv0 = __ldg(reinterpret_cast<const float4 *>(a.v_w_scale + wo));
+        wv1 = __ldg(reinterpret_cast<const float4 *>(a.v_w_scale + wo) + 1);
+    }
+    // ---- then convert, rotate, store
     const size_t bh = (size_t)b * a.H + h;
-    const size_t st_off = (bh * a.S + s) * D + c * 8;     // [B,H,S,d]
-    const size_t ca_off = (bh * a.T + s) * D + c * 8;     // [B,H,T,d]
-    *reinterpret_cast<uint4 *>(a.qh + st_off) = pack8(q);
-    store_cache8(a, a.k_cache, ca_off, k);
-    store_cache8(a, a.v_cache, ca_off, v);
-    if (!a.cache_f16) {
-        *reinterpret_cast<uint4 *>(a.kh + st_off) = pack8(k);
-        *reinterpret_cast<uint4 *>(a.vh + st_off) = pack8(v);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int s = s0 + 16 * r;
+        if (s < a.S) {
+            float q[8], k[8], v[8];
+            convert8<MODE>(rq[r], as[r], wq0, wq1, q);
+            convert8<MODE>(rk[r], as[r], wk0, wk1, k);
+            convert8<MODE>(rv[r], as[r], wv0, wv1, v);
+            if (a.freq_cis) {
+                rope8(f0[r], f1[r], q);
+                rope8(f0[r], f1[r], k);
+            }
+            const size_t st_off = (bh * a.S + s) * D + c * 8; // [B,H,S,d]
+            const size_t ca_off = (bh * a.T + s) * D + c * 8; // [B,H,T,d]
+            *reinterpret_cast<uint4 *>(a.qh + st_off) = pack8(q);
+            store_cache8(a, a.k_cache, ca_off, k);
+            store_cache8(a, a.v_cache, ca_off, v);
+            if (!a.cache_f16) {
+                *reinterpret_cast<uint4 *>(a.kh + st_off) = pack8(k);
+                *reinterpret_cast<uint4 *>(a.vh + st_off) = pack8(v);
+            }
+        }
     }
 }
 
@@ -166,9 +216,12 @@ __global__ void __launch_bounds__(256) flb_prefill_prologue_kernel(const Prefill
 // ------------------------------------------------------------------------------------------------
 struct __align__(8) PrefillBarriers {
     uint64_t q_full;
-    uint64_t k_full[KV_STAGES], v_full[KV_STAGES], kv_empty[KV_STAGES];
-    uint64_t s_full[2], s_empty[2];
-    uint64_t p_full, p_empty, o_full;
+    uint64_t k_full[K_STAGES], k_empty[K_STAGES];
+    uint64_t v_full[V_STAGES], v_empty[V_STAGES];
+    uint64_t s_full[2];  // S_j = Q.K_j^T landed in TMEM buffer j%2
+    uint64_t p_full[2];  // P_j written over S_j's columns by the 128 softmax threads (and O rescaled if needed)
+    uint64_t pv_done;    // O += P_j.V_j completed (one phase per tile)
+    uint64_t o_full;     // last P.V completed
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -176,9 +229,8 @@ struct __align__(8) PrefillBarriers {
 template <int BN> struct PrefillCfg {
     static constexpr int K_TILE_BYTES = BN * D * 2;     // K or V tile: BN keys x 128 dims fp16
     static constexpr int K_HALF = K_TILE_BYTES / 2;     // one [BN x 64] swizzled block
-    static constexpr int P_BYTES = BM * BN * 2;         // P tile: BN/64 blocks of [128 x 64]
     static constexpr uint32_t TMEM_COLS = (BN == 64) ? 256u : 512u; // S0, S1 (BN columns each) + O (128)
-    static constexpr size_t SMEM = (size_t)Q_TILE_BYTES + 2 * KV_STAGES * K_TILE_BYTES + P_BYTES + 256;
+    static constexpr size_t SMEM = (size_t)Q_TILE_BYTES + (K_STAGES + V_STAGES) * K_TILE_BYTES + 256;
 };
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -203,6 +255,13 @@ __device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, Prefill
     return false;
 }
 
+#ifdef FLB_TIMELINE
+// debug build only: per-role time stamps of one CTA, written into the (unused with an fp16 cache) K staging area
+#define TL(role, tile, k) do { if (tl_on) tl[((role) * 64 + (tile)) * 4 + (k)] = globaltimer_ns(); } while (0)
+#else
+#define TL(role, tile, k) do { } while (0)
+#endif
+
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
     flb_prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -212,16 +271,20 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
     // The 128-byte swizzle pattern is a function of address bits [4,10): tiles must start on 1 KB.
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char *sQ = smem;                                     // two [128 x 64] blocks
-    unsigned char *sK = sQ + Q_TILE_BYTES;                        // KV_STAGES tiles
-    unsigned char *sV = sK + KV_STAGES * Cfg::K_TILE_BYTES;       // KV_STAGES tiles
-    unsigned char *sP = sV + KV_STAGES * Cfg::K_TILE_BYTES;       // P
-    PrefillBarriers *pb = reinterpret_cast<PrefillBarriers *>(sP + Cfg::P_BYTES);
+    unsigned char *sK = sQ + Q_TILE_BYTES;                        // K_STAGES tiles
+    unsigned char *sV = sK + K_STAGES * Cfg::K_TILE_BYTES;        // V_STAGES tiles
+    PrefillBarriers *pb = reinterpret_cast<PrefillBarriers *>(sV + V_STAGES * Cfg::K_TILE_BYTES);
     if (smem_u32(smem) & 1023u) { // never observed; without it the MMAs would read scrambled tiles
         if (threadIdx.x == 0) atomicOr(a.status, kErrPrefillAlign);
         return;
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef FLB_TIMELINE
+    const bool tl_on = (blockIdx.x == gridDim.x / 2 + 1) && (lane == 0);
+    uint64_t *tl = reinterpret_cast<uint64_t *>(a.kh);
+    if (tl_on && warp == 0) tl[3 * 64 * 4] = globaltimer_ns();
+#endif
     const int nq = (a.S + BM - 1) / BM;
     const int bh = blockIdx.x / nq;
     const int qt = nq - 1 - (int)(blockIdx.x % nq); // heavy (late) query tiles first within a head
@@ -232,20 +295,39 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
 
     if (threadIdx.x == 0) {
         mbar_init(&pb->q_full, 1);
-        for (int s = 0; s < KV_STAGES; ++s) {
+        for (int s = 0; s < K_STAGES; ++s) {
             mbar_init(&pb->k_full[s], 1);
+            mbar_init(&pb->k_empty[s], 1);
+        }
+        for (int s = 0; s < V_STAGES; ++s) {
             mbar_init(&pb->v_full[s], 1);
-            mbar_init(&pb->kv_empty[s], 1);
+            mbar_init(&pb->v_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&pb->s_full[s], 1);
-            mbar_init(&pb->s_empty[s], 128);
+            mbar_init(&pb->p_full[s], 128);
         }
-        mbar_init(&pb->p_full, 128);
-        mbar_init(&pb->p_empty, 1);
+        mbar_init(&pb->pv_done, 1);
         mbar_init(&pb->o_full, 1);
         pb->abort_flag = 0;
         mbar_fence_init();
+        // the first loads leave before the CTA has finished setting up (no stage is in use yet)
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        mbar_arrive_expect_tx(&pb->q_full, Q_TILE_BYTES);
+        tma_load_3d(sQ, &tmQ, 0, q0, bh, &pb->q_full);
+        tma_load_3d(sQ + Q_TILE_BYTES / 2, &tmQ, 64, q0, bh, &pb->q_full);
+        for (int j = 0; j < K_STAGES && j < n_tiles; ++j) {
+            mbar_arrive_expect_tx(&pb->k_full[j], Cfg::K_TILE_BYTES);
+            tma_load_3d(sK + j * Cfg::K_TILE_BYTES, &tmK, 0, j * BN, bh, &pb->k_full[j]);
+            tma_load_3d(sK + j * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmK, 64, j * BN, bh, &pb->k_full[j]);
+        }
+        for (int j = 0; j < V_STAGES && j < n_tiles; ++j) {
+            mbar_arrive_expect_tx(&pb->v_full[j], Cfg::K_TILE_BYTES);
+            tma_load_3d(sV + j * Cfg::K_TILE_BYTES, &tmV, 0, j * BN, bh, &pb->v_full[j]);
+            tma_load_3d(sV + j * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmV, 64, j * BN, bh, &pb->v_full[j]);
+        }
     }
     if (warp == 1) {
         tmem_alloc(&pb->tmem_base, Cfg::TMEM_COLS);
@@ -259,25 +341,31 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
     const uint32_t tO = tmem + 2u * BN;
 
     if (warp == 0) {
-        // ======================= TMA producer =======================
+        // ======================= TMA producer: the K ring (Q and the first stages left at set-up) ======
         if (lane == 0) {
-            tma_prefetch_desc(&tmQ);
-            tma_prefetch_desc(&tmK);
-            tma_prefetch_desc(&tmV);
-            mbar_arrive_expect_tx(&pb->q_full, Q_TILE_BYTES);
-            tma_load_3d(sQ, &tmQ, 0, q0, bh, &pb->q_full);
-            tma_load_3d(sQ + Q_TILE_BYTES / 2, &tmQ, 64, q0, bh, &pb->q_full);
-            for (int j = 0; j < n_tiles; ++j) {
-                const int s = j & 1;
-                const uint32_t u = (uint32_t)(j >> 1);
-                if (!wait_bar(&pb->kv_empty[s], (u & 1u) ^ 1u, pb, a.status)) break;
-                const int k0 = j * BN;
+            for (int j = K_STAGES; j < n_tiles; ++j) {
+                const int s = j % K_STAGES;
+                const uint32_t u = (uint32_t)(j / K_STAGES);
+                TL(0, j, 0);
+                if (!wait_bar(&pb->k_empty[s], (u & 1u) ^ 1u, pb, a.status)) break;
+                TL(0, j, 1);
                 mbar_arrive_expect_tx(&pb->k_full[s], Cfg::K_TILE_BYTES);
-                tma_load_3d(sK + s * Cfg::K_TILE_BYTES, &tmK, 0, k0, bh, &pb->k_full[s]);
-                tma_load_3d(sK + s * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmK, 64, k0, bh, &pb->k_full[s]);
+                tma_load_3d(sK + s * Cfg::K_TILE_BYTES, &tmK, 0, j * BN, bh, &pb->k_full[s]);
+                tma_load_3d(sK + s * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmK, 64, j * BN, bh, &pb->k_full[s]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 6) {
+        // ======================= TMA producer: the V ring =======================
+        if (lane == 0) {
+            for (int j = V_STAGES; j < n_tiles; ++j) {
+                const int s = j % V_STAGES;
+                const uint32_t u = (uint32_t)(j / V_STAGES);
+                if (!wait_bar(&pb->v_empty[s], (u & 1u) ^ 1u, pb, a.status)) break;
+                TL(0, j, 2);
                 mbar_arrive_expect_tx(&pb->v_full[s], Cfg::K_TILE_BYTES);
-                tma_load_3d(sV + s * Cfg::K_TILE_BYTES, &tmV, 0, k0, bh, &pb->v_full[s]);
-                tma_load_3d(sV + s * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmV, 64, k0, bh, &pb->v_full[s]);
+                tma_load_3d(sV + s * Cfg::K_TILE_BYTES, &tmV, 0, j * BN, bh, &pb->v_full[s]);
+                tma_load_3d(sV + s * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmV, 64, j * BN, bh, &pb->v_full[s]);
             }
         }
         __syncwarp();
@@ -286,50 +374,56 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
         if (lane == 0) {
             // S = Q.K^T : A (Q) and B (K) both K-major, 128-byte swizzle, 8-row groups 1024 B apart
             constexpr uint32_t idesc_qk = umma_idesc_f16(BM, BN, false, false);
-            // O += P.V  : A (P) K-major; B (V) MN-major: 64-dim blocks K_HALF apart (LBO), 8-key groups
-            // 1024 B apart (SBO)
+            // O += P.V  : A (P) from TMEM (fp16 pairs in the columns S_j occupied); B (V) MN-major: 64-dim
+            // blocks K_HALF apart (LBO), 8-key groups 1024 B apart (SBO)
             constexpr uint32_t idesc_pv = umma_idesc_f16(BM, D, false, true);
-            const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
+            const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
             bool ok = wait_bar(&pb->q_full, 0, pb, a.status);
 
-            auto issue_pv = [&](int i) -> bool {
-                const int s = i & 1;
-                const uint32_t u = (uint32_t)(i >> 1);
-                if (!wait_bar(&pb->v_full[s], u & 1u, pb, a.status)) return false;
-                if (!wait_bar(&pb->p_full, (uint32_t)(i & 1), pb, a.status)) return false;
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t da = umma_desc_sw128(aP + (kk >> 2) * (BM * 128) + (kk & 3) * 32, 16, 1024);
-                    const uint64_t db = umma_desc_sw128(aV + s * Cfg::K_TILE_BYTES + kk * 2048, Cfg::K_HALF, 1024);
-                    umma_f16_ss(tO, da, db, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
-                }
-                umma_commit(&pb->kv_empty[s]);
-                umma_commit(&pb->p_empty);
-                return true;
-            };
-
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j & 1;
-                const uint32_t u = (uint32_t)(j >> 1);
-                if (!wait_bar(&pb->k_full[s], u & 1u, pb, a.status)) { ok = false; break; }
-                if (!wait_bar(&pb->s_empty[s], (u & 1u) ^ 1u, pb, a.status)) { ok = false; break; }
+            // The tensor pipe executes one thread's MMAs in issue order: S_0, S_1, PV_0, S_2, PV_1, ...
+            // so S_{j+2} overwrites TMEM buffer j%2 only after PV_j has read P_j from it.
+            auto issue_s = [&](int j) -> bool {
+                const int s = j & 1, ks = j % K_STAGES;
+                TL(1, j, 0);
+                if (!wait_bar(&pb->k_full[ks], (uint32_t)(j / K_STAGES) & 1u, pb, a.status)) return false;
+                TL(1, j, 1);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint64_t da = umma_desc_sw128(aQ + (kk >> 2) * (Q_TILE_BYTES / 2) + (kk & 3) * 32, 16, 1024);
-                    const uint64_t db = umma_desc_sw128(aK + s * Cfg::K_TILE_BYTES + (kk >> 2) * Cfg::K_HALF + (kk & 3) * 32, 16, 1024);
+                    const uint64_t db = umma_desc_sw128(aK + ks * Cfg::K_TILE_BYTES + (kk >> 2) * Cfg::K_HALF + (kk & 3) * 32, 16, 1024);
                     umma_f16_ss(tS[s], da, db, idesc_qk, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&pb->s_full[s]);
-                if (j >= 1) ok = issue_pv(j - 1);
+                umma_commit(&pb->k_empty[ks]);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                const uint32_t u = (uint32_t)(j >> 1);
+                if (j + 1 < n_tiles) {
+                    ok = issue_s(j + 1);
+                    if (!ok) break;
+                }
+                if (!wait_bar(&pb->v_full[s], u & 1u, pb, a.status)) { ok = false; break; }
+                TL(1, j, 2);
+                if (!wait_bar(&pb->p_full[s], u & 1u, pb, a.status)) { ok = false; break; }
+                TL(1, j, 3);
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint64_t db = umma_desc_sw128(aV + s * Cfg::K_TILE_BYTES + kk * 2048, Cfg::K_HALF, 1024);
+                    umma_f16_ts(tO, tS[s] + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(&pb->v_empty[s]);
+                umma_commit(&pb->pv_done);
             }
-            if (ok) ok = issue_pv(n_tiles - 1);
             if (ok) umma_commit(&pb->o_full);
         }
         __syncwarp();
     } else {
-        // ======================= softmax / correction / epilogue =======================
+        // ======================= softmax / correction / epilogue (warps 2-5) =======================
         const int quarter = warp & 3;                  // TMEM lane quarter this warp may access
         const int lrow = quarter * 32 + lane;          // query row inside the tile
         const int row = q0 + lrow;                     // query position
@@ -343,16 +437,17 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
             const int s = j & 1;
             const uint32_t u = (uint32_t)(j >> 1);
             const int k0 = j * BN;
+            if (warp == 2) TL(2, j, 0);
             ok = wait_bar(&pb->s_full[s], u & 1u, pb, a.status);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (warp == 2) TL(2, j, 1);
             tc_fence_after();
-            // the whole score row of this tile into registers, then hand the S buffer back
+            // the whole score row of this tile into registers
 #pragma unroll
             for (int ch = 0; ch < NCH; ++ch) tmem_ld32(tS[s] + lane_addr + ch * 32, r[ch]);
             tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(&pb->s_empty[s]);
+            if (warp == 2) TL(2, j, 2);
 
             const bool check = (causal && k0 + BN - 1 > q0) || (k0 + BN > a.S) || (a.mask_mode == 1);
             float m_tile = -INFINITY;
@@ -381,16 +476,16 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
                         m_tile = fmaxf(m_tile, x);
                     }
             }
-            // ---- the P buffer and O are free once P.V of the previous tile has completed
-            ok = wait_bar(&pb->p_empty, (uint32_t)((j & 1) ^ 1), pb, a.status);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
             if (j == 0) {
                 m_used = fmaxf(m_tile, -1e30f);
             } else {
                 const bool grow = m_tile > m_used + kRescaleThreshold;
                 if (__any_sync(0xffffffffu, grow)) {
+                    // O must hold every product up to tile j-1 before it is rescaled
+                    ok = wait_bar(&pb->pv_done, (uint32_t)((j - 1) & 1), pb, a.status);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
                     const float m_new = fmaxf(m_used, m_tile);
                     const float alpha = ex2(m_used - m_new);
                     m_used = m_new;
@@ -404,11 +499,10 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                         tmem_st32(tO + lane_addr + ch * 32, o);
                     }
-                    tmem_wait_st();
                 }
             }
-            // ---- P = exp2(x - m), row sum, fp16 P into the swizzled A-operand tile:
-            // element (lrow, c): block c/64, row lrow (128 B), 16-byte chunk ((c%64)/8) ^ (lrow%8)
+            // ---- P = exp2(x - m), row sum; fp16 pairs go back into the columns S_j came from
+            // (column c/2 of the buffer holds keys c, c+1), where the tensor core reads them as A
             const float sc = check ? 1.0f : a.scale_log2e; // slow path scaled the scores already
             const float neg_m = -m_used;
 #pragma unroll
@@ -422,19 +516,14 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
                     const __half2 h2 = __floats2half2_rn(p0, p1);
                     packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&h2);
                 }
-                unsigned char *blk = sP + (ch >> 1) * (BM * 128) + lrow * 128;
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const int chunk = ((ch & 1) * 4 + t) ^ (lrow & 7);
-                    *reinterpret_cast<uint4 *>(blk + chunk * 16) =
-                        make_uint4(packed[4 * t], packed[4 * t + 1], packed[4 * t + 2], packed[4 * t + 3]);
-                }
+                tmem_st16(tS[s] + lane_addr + ch * 16, packed);
             }
-            // P (shared memory, generic proxy) and O (TMEM) ready for the tensor core
+            tmem_wait_st();
             tc_fence_before();
-            fence_proxy_async_smem();
-            mbar_arrive(&pb->p_full);
+            mbar_arrive(&pb->p_full[s]);
+            if (warp == 2) TL(2, j, 3);
         }
+        if (warp == 2) TL(2, 63, 0);
 
         // ---- epilogue: O / l
         if (ok) {
@@ -444,38 +533,53 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
         if (ok) {
             tc_fence_after();
             const float inv = (l_sum > 0.f) ? 1.0f / l_sum : 0.f; // fully masked row -> zeros
-            const size_t obase = ((size_t)bh * a.S + row) * D;
+            // Every load has landed and every MMA has retired: the K/V rings are free.  Each warp
+            // stages its 32 rows there (padded rows: conflict-free 16-byte stores) and then writes
+            // them out with fully coalesced 16-byte stores, one or two whole rows per instruction.
+            const int esz = a.out_f16 ? 2 : 4;
+            const int rstride = D * esz + 16;
+            unsigned char *stg = sK + quarter * (32 * (D * 4 + 16));
             uint32_t o[32];
 #pragma unroll 1
             for (int ch = 0; ch < 4; ++ch) {
                 tmem_ld32(tO + lane_addr + ch * 32, o);
                 tmem_wait_ld();
-                if (row_valid) {
-                    if (a.out_f16) {
-                        uint4 *dst = reinterpret_cast<uint4 *>((__half *)a.out + obase + ch * 32);
+                unsigned char *dst = stg + lane * rstride + ch * 32 * esz;
+                if (a.out_f16) {
 #pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            uint32_t w[4];
+                    for (int t = 0; t < 4; ++t) {
+                        uint32_t w[4];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const __half2 h2 = __floats2half2_rn(__uint_as_float(o[8 * t + 2 * e]) * inv,
-                                                                     __uint_as_float(o[8 * t + 2 * e + 1]) * inv);
-                                w[e] = *reinterpret_cast<const uint32_t *>(&h2);
-                            }
-                            dst[t] = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int e = 0; e < 4; ++e) {
+                            const __half2 h2 = __floats2half2_rn(__uint_as_float(o[8 * t + 2 * e]) * inv,
+                                                                 __uint_as_float(o[8 * t + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<const uint32_t *>(&h2);
                         }
-                    } else {
-                        float4 *dst = reinterpret_cast<float4 *>((float *)a.out + obase + ch * 32);
-#pragma unroll
-                        for (int t = 0; t < 8; ++t)
-                            dst[t] = make_float4(__uint_as_float(o[4 * t]) * inv, __uint_as_float(o[4 * t + 1]) * inv,
-                                                 __uint_as_float(o[4 * t + 2]) * inv, __uint_as_float(o[4 * t + 3]) * inv);
+                        reinterpret_cast<uint4 *>(dst)[t] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 8; ++t)
+                        reinterpret_cast<float4 *>(dst)[t] =
+                            make_float4(__uint_as_float(o[4 * t]) * inv, __uint_as_float(o[4 * t + 1]) * inv,
+                                        __uint_as_float(o[4 * t + 2]) * inv, __uint_as_float(o[4 * t + 3]) * inv);
                 }
+            }
+            __syncwarp();
+            const int lanes_per_row = D * esz / 16;      // 16 (fp16) or 32 (fp32)
+            const int rows_per_it = 32 / lanes_per_row;  // 2 or 1
+            const int rsub = lane / lanes_per_row, cchunk = lane % lanes_per_row;
+            unsigned char *gout = (unsigned char *)a.out + ((size_t)bh * a.S + q0 + quarter * 32) * D * esz;
+            for (int r0 = 0; r0 < 32; r0 += rows_per_it) {
+                const int rr = r0 + rsub;
+                if (q0 + quarter * 32 + rr < a.S)
+                    *reinterpret_cast<uint4 *>(gout + (size_t)rr * D * esz + cchunk * 16) =
+                        *reinterpret_cast<const uint4 *>(stg + rr * rstride + cchunk * 16);
             }
         }
     }
 
+    if (warp == 2) TL(2, 63, 1);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -557,8 +661,13 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     if (!ok) return FLB_ERR_LAUNCH;
 
     if (cudaMemsetAsync(sc, 0, 256, stream) != cudaSuccess) return FLB_ERR_LAUNCH;
-    const size_t total = (size_t)B * S * H * 16;
-    flb_prefill_prologue_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a);
+    const size_t pro_blocks = (size_t)B * H * ((S + 16 * kRowsPerThread - 1) / (16 * kRowsPerThread));
+    if (a.input_mode == 0)
+        flb_prefill_prologue_kernel<0><<<(unsigned)pro_blocks, 256, 0, stream>>>(a);
+    else if (a.input_mode == 1)
+        flb_prefill_prologue_kernel<1><<<(unsigned)pro_blocks, 256, 0, stream>>>(a);
+    else
+        flb_prefill_prologue_kernel<2><<<(unsigned)pro_blocks, 256, 0, stream>>>(a);
     if (cudaGetLastError() != cudaSuccess) return FLB_ERR_LAUNCH;
 
     static_assert(sizeof(PrefillBarriers) <= 256, "barrier block must fit its slot");
