@@ -1,0 +1,100 @@
+/*
+ * flb_open_decoder.h — the reference-side binding: what OpenDecoder<OpType,INT8>::forward calls where
+ * fasterLlama/cuda/open_decoder.cu:138-239 used to be.
+ *
+ * The function takes OpenDecoder's own members (names as in fasterLlama/open_decoder.h:34-63) and
+ * forward()'s arguments, fills one flb_attn_params block and calls flb_attn_forward().  Buffers keep the
+ * reference's layouts: q/k/v are the int32 outputs of the three INT8 GEMMs (open_decoder.cu:105-136),
+ * the result lands in qkv_buf_ [B,H,S,d] fp32 for launchAttnQuantizedTransposeKernel (:245), the caches
+ * are the caller's [B,H,T,d] slabs.  Scratch is the run of workspace buffers the replaced code used and
+ * nothing else needs any more: query_out_buf_, key_out_buf_, value_out_fp_buf_ and qk_buf_, which
+ * OpenDecoder::initialize carves back to back (open_decoder.cu:39-42).
+ *
+ * Errors follow the reference's convention (fasterLlama/cuda/utils.h:50-80): print, then exit(1).
+ *
+ * Environment switches (read once per process, so that the unchanged DecodingSampling can be steered
+ * from outside):
+ *   FLB_CACHE_F16=1   keep the caches in fp16 inside the caller's float slabs (first half of each slab)
+ *   FLB_MASK_MODE=n   force a flb_mask_mode (default: the caller's additive mask is classified once
+ *                     with flb_attn_classify_mask and the matching index-computed mode is used)
+ */
+#ifndef FLB_OPEN_DECODER_H
+#define FLB_OPEN_DECODER_H
+
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "flb_attn.h"
+
+static inline int flb_open_decoder_env_int(const char *name, int fallback) {
+    const char *e = getenv(name);
+    return e ? atoi(e) : fallback;
+}
+
+static inline void flb_open_decoder_attention(int batch_size_, int head_num_, int size_per_head_, int max_prompt_len_,
+                                              int total_len_, int seq_len, int start_pos, const int32_t *query_buf_,
+                                              const int32_t *key_buf_, const int32_t *value_buf_,
+                                              const float *from_tensor_scale_buf_, const float *q_weight_scale,
+                                              const float *k_weight_scale, const float *v_weight_scale, const float *freq_cis,
+                                              const float *attn_mask, float *key_cache_, float *value_cache_,
+                                              float *query_out_buf_, float *qk_buf_, float *qkv_buf_, cudaStream_t stream) {
+    static int cache_f16 = -1, mask_mode = -1;
+    if (cache_f16 < 0) cache_f16 = flb_open_decoder_env_int("FLB_CACHE_F16", 0);
+    if (mask_mode < 0) {
+        mask_mode = flb_open_decoder_env_int("FLB_MASK_MODE", -1);
+        if (mask_mode < 0) {
+            if (!attn_mask) {
+                mask_mode = FLB_MASK_NONE;
+            } else {
+                // one look at the caller's mask, at the first call only (synchronises the stream once)
+                int m = FLB_MASK_GENERIC;
+                if (flb_attn_classify_mask(attn_mask, total_len_, total_len_, qk_buf_, &m, stream) != FLB_OK) m = FLB_MASK_GENERIC;
+                mask_mode = m;
+            }
+        }
+    }
+    flb_attn_params ap;
+    memset(&ap, 0, sizeof(ap));
+    ap.batch_size = batch_size_;
+    ap.head_num = head_num_;
+    ap.size_per_head = size_per_head_;
+    ap.seq_len = seq_len;
+    ap.start_pos = start_pos;
+    ap.total_len = total_len_;
+    ap.input_mode = FLB_IN_INT32;
+    ap.q = query_buf_;
+    ap.k = key_buf_;
+    ap.v = value_buf_;
+    ap.act_scale = from_tensor_scale_buf_;
+    ap.q_w_scale = q_weight_scale;
+    ap.k_w_scale = k_weight_scale;
+    ap.v_w_scale = v_weight_scale;
+    ap.freq_cis = freq_cis; /* row s of this pointer for token s: the reference's rule (decoder_kernels.cu:440) */
+    ap.rope_pos0 = 0;
+    ap.rope_add_past = 0;
+    ap.mask_mode = mask_mode;
+    ap.attn_mask = attn_mask;
+    ap.mask_row_stride = total_len_;
+    ap.k_cache = key_cache_;
+    ap.v_cache = value_cache_;
+    ap.cache_dtype = cache_f16 ? FLB_F16 : FLB_F32;
+    ap.out = qkv_buf_;
+    ap.out_dtype = FLB_F32;
+    ap.softmax_scale = 1.0f / sqrtf((float)size_per_head_);
+    /* query_out_buf_ .. end of qk_buf_: 3 * buf_size floats + the score buffer, contiguous */
+    ap.scratch = query_out_buf_;
+    ap.scratch_bytes = sizeof(float) * ((size_t)(qk_buf_ - query_out_buf_) + (size_t)batch_size_ * head_num_ * max_prompt_len_ * total_len_);
+    ap.scratch_zeroed = 0;
+    const int st = flb_attn_forward(&ap, stream);
+    if (st != FLB_OK) {
+        printf("CUDA Error:\n    File:   %s\n    Line:   %d\n    flb_attn status: %d (%s)\n", __FILE__, __LINE__, st,
+               flb_status_string(st));
+        exit(1);
+    }
+}
+
+#endif /* FLB_OPEN_DECODER_H */

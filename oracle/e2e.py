@@ -1,0 +1,136 @@
+"""End-to-end run of the reference's DecodingSampling<FP16> (random-init LLaMA-2-shaped weights, INT8
+per-channel GEMMs) through one of the two libraries built by make_e2e_variants.py:
+
+    python oracle/e2e.py --variant ref|flb --config small|c5 --out ids.npz [--cache-f16] [--mask strict|inclusive]
+
+`ref` = the reference's own attention (gemv arguments corrected), `flb` = the same classes with the
+attention section replaced by the drop-in adaptor.  TEST / BASELINE INFRASTRUCTURE.  Weights are
+drawn here with torch (seeded), quantised per output channel, and handed to the reference as device
+pointers; the reference does everything else."""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+CONFIGS = {
+    # the reference's sample sizes (samples/llama_fp16.cu:348-357), top-k instead of top-p
+    "small": dict(batch=4, head_num=8, size_per_head=128, vocab=200, max_prompt_len=16, max_gen_len=16, layers=4, ffn=256, topk=4, seed=4),
+    "medium": dict(batch=8, head_num=32, size_per_head=128, vocab=2000, max_prompt_len=160, max_gen_len=48, layers=4, ffn=1024, topk=4, seed=4),
+    # LLaMA-2-7B: 32 layers, hidden 4096, 32 heads, FFN 11008, vocab 32000; batch 32, prompt 512, 256 new tokens, top-k 4, seed 4
+    "c5": dict(batch=32, head_num=32, size_per_head=128, vocab=32000, max_prompt_len=512, max_gen_len=256, layers=32, ffn=11008, topk=4, seed=4),
+}
+
+
+class Layer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("attn_gamma", "wq", "wk", "wv", "wo", "sq", "sk", "sv", "so", "ffn_gamma", "w1", "w2", "w3", "s1", "s2", "s3")]
+
+
+class Args(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("batch", "max_prompt_len", "max_gen_len", "head_num", "size_per_head", "vocab", "layers", "end_id", "ffn", "topk")] + [
+        ("topp", C.c_float), ("device", C.c_int), ("layer", C.POINTER(Layer)), ("attn_mask", C.c_void_p), ("embedding", C.c_void_p),
+        ("freq_cis", C.c_void_p), ("prompt_seq_len", C.c_void_p), ("min_prompt", C.c_int), ("max_prompt", C.c_int),
+        ("prompt_tokens", C.c_void_p), ("prompt_mask", C.c_void_p), ("final_gamma", C.c_void_p), ("lm_head", C.c_void_p),
+        ("output_ids", C.c_void_p), ("seq_len", C.c_void_p)]
+
+
+def quantise(w: torch.Tensor):
+    """Symmetric per-output-channel INT8 of a row-major [in, out] matrix: scale[n] = absmax_k / 127."""
+    scale = (w.abs().amax(dim=0) / 127.0).clamp_min(1e-12)
+    q = torch.round(w / scale).clamp_(-127, 127).to(torch.int8)
+    return q.contiguous(), scale.float().contiguous()
+
+
+def run(variant: str, cfg: dict, mask: str = "inclusive", device: int = 0):
+    lib = C.CDLL(os.path.join(HERE, "_ref", f"libe2e_{variant}.so"))
+    lib.e2e_run.restype = C.c_int
+    lib.e2e_run.argtypes = [C.POINTER(Args), C.POINTER(C.c_float)]
+    dev = f"cuda:{device}"
+    g = torch.Generator(device=dev)
+    g.manual_seed(cfg["seed"])
+    hidden = cfg["head_num"] * cfg["size_per_head"]
+    T = cfg["max_prompt_len"] + cfg["max_gen_len"]
+    keep = []
+
+    def dense(i, o):
+        w = torch.randn((i, o), generator=g, device=dev) * 0.02
+        q, s = quantise(w)
+        keep.extend([q, s])
+        return q.data_ptr(), s.data_ptr()
+
+    layers = (Layer * cfg["layers"])()
+    for l in range(cfg["layers"]):
+        ga = torch.ones(hidden, dtype=torch.float16, device=dev)
+        gf = torch.ones(hidden, dtype=torch.float16, device=dev)
+        keep.extend([ga, gf])
+        layers[l].attn_gamma, layers[l].ffn_gamma = ga.data_ptr(), gf.data_ptr()
+        layers[l].wq, layers[l].sq = dense(hidden, hidden)
+        layers[l].wk, layers[l].sk = dense(hidden, hidden)
+        layers[l].wv, layers[l].sv = dense(hidden, hidden)
+        layers[l].wo, layers[l].so = dense(hidden, hidden)
+        layers[l].w1, layers[l].s1 = dense(hidden, cfg["ffn"])
+        layers[l].w3, layers[l].s3 = dense(hidden, cfg["ffn"])
+        layers[l].w2, layers[l].s2 = dense(cfg["ffn"], hidden)
+    emb = (torch.randn((cfg["vocab"], hidden), generator=g, device=dev) * 0.02).half()
+    head = (torch.randn((hidden, cfg["vocab"]), generator=g, device=dev) * 0.02).half()
+    fg = torch.ones(hidden, dtype=torch.float16, device=dev)
+    B, P = cfg["batch"], cfg["max_prompt_len"]
+    prompts = torch.randint(3, cfg["vocab"], (B, P), generator=g, device=dev, dtype=torch.int32)
+    pmask = torch.ones((B, P), dtype=torch.bool, device=dev)
+    plen = torch.full((B,), P, dtype=torch.int32, device=dev)
+    r = torch.arange(T, device=dev)
+    vis = (r[None, :] < r[:, None]) if mask == "strict" else (r[None, :] <= r[:, None])
+    amask = torch.where(vis, 0.0, -torch.finfo(torch.float32).max).float().contiguous()
+    freq = torch.zeros((T, cfg["size_per_head"]), dtype=torch.float32, device=dev)
+    out_ids = torch.zeros((B, T), dtype=torch.int32, device=dev)
+    seq_len = torch.zeros((B,), dtype=torch.int32, device=dev)
+    torch.cuda.synchronize()
+
+    a = Args()
+    for n in ("batch", "max_prompt_len", "max_gen_len", "head_num", "size_per_head", "vocab", "layers", "ffn", "topk"):
+        setattr(a, n, cfg[n])
+    a.end_id, a.topp, a.device = 2, 0.0, device
+    a.layer = layers
+    a.attn_mask, a.embedding, a.freq_cis = amask.data_ptr(), emb.data_ptr(), freq.data_ptr()
+    a.prompt_seq_len, a.min_prompt, a.max_prompt = plen.data_ptr(), P, P
+    a.prompt_tokens, a.prompt_mask = prompts.data_ptr(), pmask.data_ptr()
+    a.final_gamma, a.lm_head = fg.data_ptr(), head.data_ptr()
+    a.output_ids, a.seq_len = out_ids.data_ptr(), seq_len.data_ptr()
+    ms = C.c_float(0)
+    st = lib.e2e_run(C.byref(a), C.byref(ms))
+    torch.cuda.synchronize()
+    if st != 0:
+        raise RuntimeError(f"e2e_run status {st}")
+    return out_ids.cpu().numpy(), seq_len.cpu().numpy(), float(ms.value)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--variant", required=True, choices=["ref", "flb", "ref32", "mix"])
+    ap.add_argument("--config", default="small", choices=sorted(CONFIGS))
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--mask", default="inclusive", choices=["inclusive", "strict"])
+    ap.add_argument("--cache-f16", action="store_true")
+    ap.add_argument("--repeat", type=int, default=1, help="runs; the time of the last one is reported")
+    args = ap.parse_args()
+    if args.cache_f16:
+        os.environ["FLB_CACHE_F16"] = "1"
+    cfg = CONFIGS[args.config]
+    for _ in range(args.repeat):
+        ids, sl, ms = run(args.variant, cfg, mask=args.mask)
+    np.savez(args.out, ids=ids, seq_len=sl, ms=ms)
+    toks = cfg["batch"] * cfg["max_gen_len"]
+    print(json.dumps({"variant": args.variant, "config": args.config, "mask": args.mask, "cache_f16": bool(args.cache_f16),
+                      "ms": round(ms, 2), "tokens_per_s": round(toks / ms * 1e3, 1), "first_ids": ids[0, :8].tolist(),
+                      "seq_len": sl[:4].tolist()}))
+
+
+if __name__ == "__main__":
+    main()

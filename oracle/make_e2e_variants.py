@@ -1,0 +1,173 @@
+"""Builds two end-to-end libraries from a PATCHED COPY of the reference checkout (nothing of the
+reference is committed here; the copy lives under oracle/_ref/, which is git-ignored):
+
+  oracle/_ref/libe2e_ref.so   the reference's DecodingSampling + OpenDecoder with
+        (1) size_t instead of int for the buffer sizes that overflow 32 bits at LLaMA-2-7B sizes
+            (decoding_sampling.cu: cache/workspace/slab sizes; open_decoder.{h,cu}: getWorkspaceSize), and
+        (2) the two decode gemv calls given the arguments the code intends (as written they are
+            rejected by cuBLAS for L > size_per_head): OP_T m=d n=L, score stride L.
+  oracle/_ref/libe2e_flb.so   the same with (1) and, instead of (2), lines 138-239 of open_decoder.cu
+        (the whole attention section) replaced by one call of flb_open_decoder_attention()
+        (include/flb_open_decoder.h) — the drop-in adaptor.
+
+  oracle/_ref/libe2e_ref32.so like libe2e_ref.so, but with the prefill GEMMs computing in true fp32
+        (CUBLAS_COMPUTE_32F instead of CUBLAS_COMPUTE_32F_FAST_16F in common.h) — used only to measure how far
+        the reference's own fp16 tensor-core rounding moves its sampled tokens.
+
+All are linked with oracle/e2e_runner.cu.  TEST / BASELINE INFRASTRUCTURE.
+usage: python oracle/make_e2e_variants.py [reference-root]"""
+from __future__ import annotations
+
+import os
+import re
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+OUT = os.path.join(HERE, "_ref")
+
+
+def _sub(text: str, pattern: str, repl: str, count: int, what: str) -> str:
+    new, n = re.subn(pattern, repl, text, flags=re.S)
+    if n != count:
+        raise RuntimeError(f"patch '{what}': expected {count} match(es), found {n}")
+    return new
+
+
+def patch_sizes(src: str) -> None:
+    p = os.path.join(src, "open_decoder.h")
+    t = open(p).read()
+    t = _sub(t, r"int getWorkspaceSize\(\);", "size_t getWorkspaceSize();", 1, "header return type")
+    open(p, "w").write(t)
+    p = os.path.join(src, "cuda", "open_decoder.cu")
+    t = open(p).read()
+    t = _sub(t, r"\n    int OpenDecoder<OpType_, QuantizationType>::getWorkspaceSize\(\)", "\n    size_t OpenDecoder<OpType_, QuantizationType>::getWorkspaceSize()", 1, "definition return type")
+    t = _sub(t, r"int work_space_size =", "size_t work_space_size =", 1, "work_space_size")
+    open(p, "w").write(t)
+    p = os.path.join(src, "cuda", "decoding_sampling.cu")
+    t = open(p).read()
+    for name, cnt in (("decoder_workspace_size", 1), ("cache_size", 2), ("datatype_buf_size", 1), ("float_buf_size", 1), ("int_buf_size", 1)):
+        t = _sub(t, rf"\bint {name} =", f"size_t {name} =", cnt, name)
+    open(p, "w").write(t)
+
+
+def attention_section(lines: list[str]) -> tuple[int, int]:
+    """0-based [start, end) of open_decoder.cu:138-239, checked against its anchors."""
+    start, end = 137, 239
+    if "Quantized-rope" not in lines[start + 1] or lines[end - 1].strip() != "}" or "quantized qkv to int8" not in lines[end + 2]:
+        raise RuntimeError("open_decoder.cu does not look like the surveyed revision (attention section anchors moved)")
+    return start, end
+
+
+def patch_gemv(src: str) -> None:
+    p = os.path.join(src, "cuda", "open_decoder.cu")
+    t = open(p).read()
+    t = _sub(t, r"CUBLAS_OP_T,\s*seq_len \+ start_pos, size_per_head_,", "CUBLAS_OP_T,\n size_per_head_, seq_len + start_pos,", 1, "gemv-1 m/n")
+    t = _sub(t, r"qk_buf_, 1, size_per_head_,(\s*)batch_size_ \* head_num_\)\);", r"qk_buf_, 1, seq_len + start_pos,\1batch_size_ * head_num_));", 1, "gemv-1 score stride")
+    t = _sub(t, r"qk_buf_, 1, size_per_head_,(\s*)&qkv_beta,", r"qk_buf_, 1, seq_len + start_pos,\1&qkv_beta,", 1, "gemv-2 score stride")
+    open(p, "w").write(t)
+
+
+def patch_adaptor(src: str) -> None:
+    p = os.path.join(src, "cuda", "open_decoder.cu")
+    lines = open(p).read().split("\n")
+    s, e = attention_section(lines)
+    call = """            flb_open_decoder_attention(batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
+                                       query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
+                                       param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
+                                       param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
+                                       key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, param_.stream);"""
+    lines[s:e] = call.split("\n")
+    text = "\n".join(lines)
+    text = text.replace('#include "open_decoder.h"', '#include "open_decoder.h"\n#include "flb_open_decoder.h"', 1)
+    open(p, "w").write(text)
+
+
+def patch_mix(src: str) -> None:
+    """Diagnostic variant: the corrected reference section is kept and the adaptor call is added in front of
+    it; the environment variable FLB_E2E_USE picks per call which one runs (bit 0: decode calls use the
+    adaptor, bit 1: prefill calls use the adaptor)."""
+    patch_gemv(src)
+    p = os.path.join(src, "cuda", "open_decoder.cu")
+    lines = open(p).read().split("\n")
+    s, e = attention_section(lines)
+    head = """            static const int flb_use = getenv("FLB_E2E_USE") ? atoi(getenv("FLB_E2E_USE")) : 3;
+            if ((seq_len > 1) ? (flb_use & 2) : (flb_use & 1)) {
+            flb_open_decoder_attention(batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
+                                       query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
+                                       param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
+                                       param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
+                                       key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, param_.stream);
+            } else {"""
+    tail = """            }
+            if ((flb_use & 4) && seq_len == 1) {
+                // diagnostic: run the adaptor on the same inputs after the reference section and report the difference
+                static int ncmp = 0;
+                const size_t n = (size_t)batch_size_ * head_num_ * seq_len * size_per_head_;
+                std::vector<float> h_ref(n), h_flb(n);
+                cudaStreamSynchronize(param_.stream);
+                cudaMemcpy(h_ref.data(), qkv_buf_, n * sizeof(float), cudaMemcpyDeviceToHost);
+                flb_open_decoder_attention(batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
+                                       query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
+                                       param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
+                                       param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
+                                       key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, param_.stream);
+                cudaStreamSynchronize(param_.stream);
+                cudaMemcpy(h_flb.data(), qkv_buf_, n * sizeof(float), cudaMemcpyDeviceToHost);
+                cudaMemcpy(qkv_buf_, h_ref.data(), n * sizeof(float), cudaMemcpyHostToDevice);
+                double mx = 0, amax = 0; size_t at = 0;
+                for (size_t i = 0; i < n; ++i) { double d = fabs((double)h_ref[i] - h_flb[i]); if (d > mx) { mx = d; at = i; } amax = fmax(amax, fabs((double)h_ref[i])); }
+                if (ncmp < 70) printf("[cmp %d] start_pos %d max|ref-flb| %.3e at %zu (ref %.6f flb %.6f) max|ref| %.3f\\n", ncmp, start_pos, mx, at, h_ref[at], h_flb[at], amax);
+                ++ncmp;
+            }"""
+    lines[s:e] = head.split("\n") + lines[s:e] + tail.split("\n")
+    text = "\n".join(lines)
+    text = text.replace('#include "open_decoder.h"', '#include <vector>\n#include <cmath>\n#include "open_decoder.h"', 1)
+    text = text.replace('#include "open_decoder.h"', '#include "open_decoder.h"\n#include "flb_open_decoder.h"', 1)
+    open(p, "w").write(text)
+
+
+def build(name: str, ref_root: str) -> str:
+    vdir = os.path.join(OUT, "variants", name)
+    if os.path.isdir(vdir):
+        shutil.rmtree(vdir)
+    src = os.path.join(vdir, "fasterLlama")
+    shutil.copytree(os.path.join(ref_root, "fasterLlama"), src, ignore=shutil.ignore_patterns("lib", "*.so"))
+    os.chmod(src, 0o755)
+    for r, ds, fs in os.walk(src):
+        for x in ds + fs:
+            os.chmod(os.path.join(r, x), 0o755 if x in ds else 0o644)
+    patch_sizes(src)
+    if name in ("ref", "ref32"):
+        patch_gemv(src)
+    elif name == "mix":
+        patch_mix(src)
+    else:
+        patch_adaptor(src)
+    if name == "ref32":
+        p = os.path.join(src, "cuda", "common.h")
+        t = open(p).read()
+        t = _sub(t, r"CUBLAS_COMPUTE_32F_FAST_16F", "CUBLAS_COMPUTE_32F", 1, "fp32 prefill math")
+        open(p, "w").write(t)
+    lib = os.path.join(OUT, f"libe2e_{name}.so")
+    cu = [os.path.join(src, "cuda", f) for f in ("decoder_kernels.cu", "decoding_kernels.cu", "open_decoder.cu", "decoding_sampling.cu")]
+    cmd = ["nvcc", "-std=c++17", "-O3", "-DNDEBUG", "-w", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
+           "-shared", "-cudart", "shared", "-I", src, "-I", os.path.join(src, "cuda"), "-I", os.path.join(ROOT, "include"),
+           *cu, os.path.join(HERE, "e2e_runner.cu"), "-lcublas", "-lcurand", "-o", lib]
+    if name in ("flb", "mix"):
+        pkg = os.path.join(ROOT, "fasterllama_b200")
+        cmd += ["-L", pkg, "-lflb_attn", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../fasterllama_b200"]
+    subprocess.run(cmd, check=True)
+    return lib
+
+
+def main(ref_root: str = "/root/reference") -> None:
+    os.makedirs(OUT, exist_ok=True)
+    for name in (sys.argv[2:] or ["ref", "flb", "ref32"]):
+        print("built", build(name, ref_root))
+
+
+if __name__ == "__main__":
+    main(*sys.argv[1:2])
