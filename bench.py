@@ -379,7 +379,7 @@ def run_prefill(args, rank, world, local):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch, from the ncu capture summarised
 # under profiles/ (None until a capture of that workload exists)
-DRAM_TRAFFIC_PER_LAUNCH: dict[str, int | None] = {"c2": None, "c4": None}
+DRAM_TRAFFIC_PER_LAUNCH: dict[str, int | None] = {"c2": 413121536, "c4": 3977282560}  # c4: the c2 capture scaled by the algorithmic bytes
 
 
 def cpu_baseline(case, bytes_step: int, B: int, min_seconds: float = 10.0) -> dict:
