@@ -81,3 +81,46 @@ def test_two_gloo_ranks_reproduce_the_unsharded_result(shape):
     axis, ok = ret.get(timeout=10)
     assert ok
     assert axis == ("batch" if shape[0] % 2 == 0 else "head")
+
+
+def _tp_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from fasterllama_b200.tensor_parallel import HeadShardedAttention
+        from util import run_oracle
+
+        B, H = 3, 8
+        case = W.host_case("tp", 9, B, H, 600, past=np.array([555, 12, 300], dtype=np.int32), in_dtype="int32")
+        full = run_oracle(case)["out"]
+
+        def attend(loc):  # the host oracle stands in for the device call
+            arrays = {k: (v.numpy() if isinstance(v, torch.Tensor) else v) for k, v in loc.items()}
+            part = W.Case(name="p", B=B, H=H // world, S=1, T=case.T, start_pos=0, arrays=arrays, rope_add_past=True,
+                          mask_mode=case.mask_mode, max_past_len=case.max_past_len)
+            loc["out"] = torch.from_numpy(run_oracle(part)["out"])
+
+        layer = HeadShardedAttention(B, H, world, rank, attend)
+        loc = layer.local_arrays({k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in case.arrays.items()})
+        got = layer.forward(loc).numpy()
+        if rank == 0:
+            ret.put(bool(np.array_equal(got, full)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_sharded_layer_gathers_the_unsharded_result():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert ret.get(timeout=10)

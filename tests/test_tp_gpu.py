@@ -1,0 +1,72 @@
+"""Head-sharded attention layer on two GPUs (NCCL): each rank runs the CUDA path on half of the heads,
+the head outputs are all-gathered, and the result must be bit-identical to the unsharded call.
+Skipped on a box with fewer than two GPUs."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    try:
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from fasterllama_b200 import attention as A
+        from fasterllama_b200 import workloads as W
+        from fasterllama_b200.tensor_parallel import HeadShardedAttention
+
+        dev = f"cuda:{rank}"
+        B, H, T = 4, 16, 1300
+        lens = np.array([1200, 37, 512, 700], dtype=np.int32)
+        case = W.host_case("tp-gpu", 13, B, H, T, past=lens, in_dtype="float16", cache_dtype="float16", out_dtype="float32")
+        full_dev = W.to_device(case, dev)
+        A.forward(case.params(full_dev))
+        torch.cuda.synchronize()
+        want = full_dev["out"].clone()
+
+        def attend(loc):
+            part = W.Case(name="p", B=B, H=H // world, S=1, T=T, start_pos=0, arrays=loc, rope_add_past=True,
+                          mask_mode=case.mask_mode, max_past_len=case.max_past_len)
+            loc["scratch"] = torch.empty(A.workspace_bytes(B, H // world, T), dtype=torch.uint8, device=dev)
+            A.forward(part.params(loc))
+
+        layer = HeadShardedAttention(B, H, world, rank, attend)
+        fresh = W.to_device(case, dev)
+        fresh.pop("scratch")
+        got = layer.forward(layer.local_arrays(fresh))
+        torch.cuda.synchronize()
+        ok = torch.equal(got, want)
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            ret.put(bool(flag.item()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_head_sharded_layer_on_two_gpus(cuda_device):
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    assert ret.get(timeout=10)
