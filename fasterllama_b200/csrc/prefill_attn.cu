@@ -463,18 +463,31 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
                 int lim = min(BN, a.S - k0);
                 if (a.mask_mode == 2) lim = min(lim, row - k0 + 1);
                 if (a.mask_mode == 3) lim = min(lim, row - k0);
-                const float *mrow = (a.mask_mode == 1 && row_valid) ? a.attn_mask + (size_t)row * a.mask_row_stride + k0 : nullptr;
+                if (a.mask_mode != 1) {
+                    // causal diagonal / end of the prompt: an index test per key, no mask loads
 #pragma unroll
-                for (int ch = 0; ch < NCH; ++ch)
+                    for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int c = ch * 32 + i;
-                        float x = __uint_as_float(r[ch][i]) * a.scale_log2e;
-                        if (mrow && c < lim) x += __ldg(mrow + c) * kLog2e;
-                        if (c >= lim) x = -INFINITY;
-                        r[ch][i] = __float_as_uint(x);
-                        m_tile = fmaxf(m_tile, x);
-                    }
+                        for (int i = 0; i < 32; ++i) {
+                            const float x = (ch * 32 + i < lim) ? __uint_as_float(r[ch][i]) * a.scale_log2e : -INFINITY;
+                            r[ch][i] = __float_as_uint(x);
+                            m_tile = fmaxf(m_tile, x);
+                        }
+                } else {
+                    // the caller's additive mask, row = query position (rows beyond the prompt see nothing)
+                    const float *mrow = a.attn_mask + (size_t)min(row, a.S - 1) * a.mask_row_stride + k0;
+                    if (!row_valid) lim = 0;
+#pragma unroll
+                    for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int c = ch * 32 + i;
+                            float x = -INFINITY;
+                            if (c < lim) x = fmaf(__ldg(mrow + c), kLog2e, __uint_as_float(r[ch][i]) * a.scale_log2e);
+                            r[ch][i] = __float_as_uint(x);
+                            m_tile = fmaxf(m_tile, x);
+                        }
+                }
             }
             if (j == 0) {
                 m_used = fmaxf(m_tile, -1e30f);

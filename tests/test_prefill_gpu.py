@@ -27,14 +27,14 @@ def _check(case, cuda, orc, cache16):
     assert not cuda["k_cache"][:, :, S:].any() and not cuda["v_cache"][:, :, S:].any()
 
 
-@pytest.mark.parametrize("S", [2, 17, 64, 127, 128, 129, 200, 256, 300, 513])
+@pytest.mark.parametrize("S", [2, 17, 64, 127, 128, 129, 200, 255, 256, 257, 300, 383, 384, 385, 513, 640, 1000])
 def test_prefill_lengths_fp16_cache(cuda_device, S):
     case = W.host_case(f"pf16-S{S}", 400 + S, 1, 2, S + 40, S=S, past=0, in_dtype="float16", cache_dtype="float16",
                        out_dtype="float32", rope="past")
     _check(case, run_cuda(case), run_oracle(case), cache16=True)
 
 
-@pytest.mark.parametrize("S", [5, 128, 260])
+@pytest.mark.parametrize("S", [5, 128, 260, 520])
 def test_prefill_fp32_cache_int32_inputs(cuda_device, S):
     """The reference's data path: int32 accumulators + scales in, fp32 cache, fp32 output.  The
     tensor cores take fp16 operands (as the reference's own FAST_16F GEMMs do), so the oracle is
@@ -44,7 +44,7 @@ def test_prefill_fp32_cache_int32_inputs(cuda_device, S):
 
 
 @pytest.mark.parametrize("mask_mode", [A.FLB_MASK_NONE, A.FLB_MASK_GENERIC, A.FLB_MASK_CAUSAL_INCLUSIVE, A.FLB_MASK_CAUSAL_STRICT])
-@pytest.mark.parametrize("S", [100, 256])
+@pytest.mark.parametrize("S", [100, 256, 400])
 def test_prefill_mask_modes(cuda_device, mask_mode, S):
     case = W.host_case(f"pmask{mask_mode}-S{S}", 600 + S, 1, 4, S + 3, S=S, past=0, in_dtype="float32", cache_dtype="float16",
                        mask_mode=mask_mode)
