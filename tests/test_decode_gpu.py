@@ -130,3 +130,37 @@ def test_head_sharding_is_bit_identical(cuda_device):
         part.H = 4
         got = run_cuda(part)["out"]
         assert np.array_equal(got, out_full[:, hs])
+
+
+def test_out_of_range_length_is_flagged_not_followed(cuda_device):
+    """A per-sequence length outside [0, total_len - 1] (a caller bug) must not make the kernel read or
+    write outside the cache slab: the length is clamped, the call completes, and the status word at the
+    head of the scratch reports it (bit 4) for the host to read."""
+    import torch
+    lens = np.array([100, 50], dtype=np.int32)
+    case = W.host_case("badlen", 51, 2, 4, 256, past=lens)
+    dev = W.to_device(case)
+    guard = 0xA5
+    # canaries either side of the caches: the clamped kernel must leave them alone
+    for n in ("k_cache", "v_cache"):
+        buf = torch.full((dev[n].numel() + 4096,), float("nan"), device="cuda")
+        buf[2048:2048 + dev[n].numel()] = dev[n].flatten()
+        dev[n + "_buf"] = buf
+        dev[n] = buf[2048:2048 + dev[n].numel()].view(dev[n].shape)
+    dev["past_lens"] = torch.tensor([100, 100000], dtype=torch.int32, device="cuda")  # second entry is nonsense
+    case.max_past_len = 255
+    p = case.params(dev)
+    A.forward(p)
+    torch.cuda.synchronize()
+    assert A.scratch_status(dev["scratch"]) & 4, "the bad length was not reported"
+    for n in ("k_cache_buf", "v_cache_buf"):
+        assert torch.isnan(dev[n][:2048]).all() and torch.isnan(dev[n][-2048:]).all(), "write outside the cache slab"
+    # the well-formed sequence is still right
+    good = W.host_case("badlen", 51, 2, 4, 256, past=lens)
+    orc = run_oracle(good)
+    assert_fp32_close(dev["out"][0].cpu().numpy(), orc["out"][0], what="sequence with a valid length")
+    # and the next, well-formed call on the same scratch is clean again
+    dev["past_lens"] = torch.from_numpy(lens).cuda()
+    A.forward(case.params(dev))
+    torch.cuda.synchronize()
+    assert A.scratch_status(dev["scratch"]) == 0
