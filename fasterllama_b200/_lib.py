@@ -64,6 +64,8 @@ class FlbAttnParams(C.Structure):
         ("scratch_bytes", C.c_size_t),
         ("scratch_zeroed", C.c_int),
         ("split_len", C.c_int),
+        ("out_q8", C.c_void_p),
+        ("out_q8_scale", C.c_void_p),
     ]
 
 
@@ -109,7 +111,7 @@ def load_library(path: str | None = None) -> C.CDLL:
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.restype = res
         fn.argtypes = args
-    if lib.flb_attn_abi_version() != 1:
+    if lib.flb_attn_abi_version() != 2:
         raise RuntimeError("libflb_attn.so has an unexpected ABI version")
     if path is None:
         _lib = lib

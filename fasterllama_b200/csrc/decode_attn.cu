@@ -80,6 +80,50 @@ __device__ __forceinline__ float load_input(const DecodeArgs &a, const void *bas
 
 } // namespace
 
+// Fused form of the reference's launchAttnQuantizedTransposeKernel (decoder_kernels.cu:1179-1255) for
+// seq_len == 1: called by every CTA that has just written a head's final output.  The one that is last
+// for its sequence (an arrival counter per sequence; nobody waits) reads the whole [H, d] fp32 row back,
+// takes absmax over all heads with the reference's -1e9f floor, writes absmax / 127 and the codes
+// cvt.rni.sat.s8(x * 127.0f / absmax) as [H*d].  All threads of the CTA must call it.
+template <int NWARPS>
+__device__ __forceinline__ void quantize_row_if_last(const DecodeArgs &a, int b, float *red, int *flag) {
+    constexpr int D = kHeadDim;
+    const int tid = threadIdx.x;
+    __syncthreads(); // the head's output stores precede the fence of thread 0
+    if (tid == 0) {
+        __threadfence();
+        const unsigned old = atomicAdd(a.row_counters + b, 1u);
+        *flag = (old == (unsigned)(a.H - 1));
+    }
+    __syncthreads();
+    if (!*flag) return;
+    __threadfence();
+    const float *row = (const float *)a.out + (size_t)b * a.H * D;
+    float amax = -1e9f;
+    if (tid < D)
+        for (int h = 0; h < a.H; ++h) amax = fmaxf(amax, fabsf(__ldcg(row + (size_t)h * D + tid)));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if (tid < D && (tid & 31) == 0) red[tid >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int w = 1; w < D / 32; ++w) amax = fmaxf(amax, red[w]);
+    if (tid == 0) {
+        a.out_q8_scale[b] = amax / 127.0f;
+        a.row_counters[b] = 0u; // ready for the next call
+    }
+    if (tid < D) {
+        int8_t *dst = a.out_q8 + (size_t)b * a.H * D;
+        for (int h = 0; h < a.H; ++h) {
+            const float x = __ldcg(row + (size_t)h * D + tid) * 127.0f / amax;
+            int q;
+            asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(x));
+            dst[(size_t)h * D + tid] = (int8_t)q;
+        }
+    }
+}
+
 template <typename CacheT, int TILE_ROWS, int STAGES, int NWARPS>
 __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(const __grid_constant__ DecodeArgs a) {
     constexpr int D = kHeadDim;
@@ -351,6 +395,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
             else
                 ((float *)a.out)[oo] = r;
         }
+        if (a.out_q8) quantize_row_if_last<NWARPS>(a, b, red, flag);
         return;
     }
 
@@ -389,6 +434,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
             ((float *)a.out)[oo] = r;
         if (tid == 0) a.counters[unit] = 0u; // ready for the next call
     }
+    if (a.out_q8) quantize_row_if_last<NWARPS>(a, b, red, flag);
 }
 
 // ---- host-side launcher ------------------------------------------------------------------

@@ -36,6 +36,9 @@ struct DecodeArgs {
     float scale_log2e;  // softmax_scale * log2(e)
     unsigned *status;   // [kStatusWords]
     unsigned *counters; // [B*H] arrivals per (b,h); zero on entry, zero on exit
+    unsigned *row_counters; // [B] heads finished per sequence (fused quantisation); zero on entry and exit
+    int8_t *out_q8;         // optional [B, H*d] int8 codes of the output row
+    float *out_q8_scale;    // optional [B]
     float *part_o;      // [B*H, nsplit_max, d]
     float *part_ml;     // [B*H, nsplit_max, 2]  (running max in the log2 domain, sum)
 };

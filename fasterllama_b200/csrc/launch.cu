@@ -27,7 +27,8 @@ struct ScratchLayout {
 inline ScratchLayout layout_for(int B, int H, int nsplit_max) {
     ScratchLayout l;
     const size_t units = (size_t)B * H;
-    l.counter_bytes = round_up(sizeof(unsigned) * (flb::kStatusWords + units), 256);
+    // status words, one arrival counter per (b,h) (partition merge), one per sequence (fused quantisation)
+    l.counter_bytes = round_up(sizeof(unsigned) * (flb::kStatusWords + units + (size_t)B), 256);
     l.ml_off = l.counter_bytes;
     l.o_off = l.ml_off + round_up(units * nsplit_max * 2 * sizeof(float), 256);
     l.total = l.o_off + units * nsplit_max * flb::kHeadDim * sizeof(float);
@@ -57,6 +58,9 @@ int check_common(const flb_attn_params *p) {
         !aligned16(p->v))
         return FLB_ERR_MISALIGNED;
     if ((size_t)p->batch_size * p->head_num > (size_t)1 << 24) return FLB_ERR_TOO_LARGE;
+    if ((p->out_q8 != nullptr) != (p->out_q8_scale != nullptr)) return FLB_ERR_NULL_POINTER;
+    if (p->out_q8 && p->out_dtype != FLB_F32) return FLB_ERR_UNSUPPORTED;
+    if (p->out_q8 && !aligned16(p->out_q8)) return FLB_ERR_MISALIGNED;
     return FLB_OK;
 }
 
@@ -174,6 +178,9 @@ int flb_attn_decode(const flb_attn_params *p, void *cuda_stream) {
     a.scale_log2e = p->softmax_scale * 1.4426950408889634f;
     a.status = reinterpret_cast<unsigned *>(sc);
     a.counters = reinterpret_cast<unsigned *>(sc) + flb::kStatusWords;
+    a.row_counters = a.counters + (size_t)p->batch_size * p->head_num;
+    a.out_q8 = p->out_q8;
+    a.out_q8_scale = p->out_q8_scale;
     a.part_ml = reinterpret_cast<float *>(sc + l.ml_off);
     a.part_o = reinterpret_cast<float *>(sc + l.o_off);
 

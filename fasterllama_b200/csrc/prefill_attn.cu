@@ -602,6 +602,32 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
 }
 
 // ------------------------------------------------------------------------------------------------
+// optional epilogue: the reference's attention-output quantisation + transpose
+// ------------------------------------------------------------------------------------------------
+// launchAttnQuantizedTransposeKernel (decoder_kernels.cu:1179-1300) restated: one block per token row
+// (b, s); absmax over all heads (floor -1e9f), scale = absmax / 127, codes cvt.rni.sat.s8(x*127/absmax),
+// [B,H,S,d] fp32 -> [B,S,H*d] int8.
+__global__ void __launch_bounds__(128) flb_attn_quant_transpose_kernel(const float *__restrict__ attn, int8_t *__restrict__ q8,
+                                                                      float *__restrict__ scale, int H, int S) {
+    __shared__ float red[4];
+    const int s = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    float amax = -1e9f;
+    for (int h = 0; h < H; ++h) amax = fmaxf(amax, fabsf(attn[(((size_t)b * H + h) * S + s) * D + tid]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((tid & 31) == 0) red[tid >> 5] = amax;
+    __syncthreads();
+    amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    if (tid == 0) scale[(size_t)b * S + s] = amax / 127.0f;
+    for (int h = 0; h < H; ++h) {
+        const float x = attn[(((size_t)b * H + h) * S + s) * D + tid] * 127.0f / amax;
+        int q;
+        asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(x));
+        q8[(((size_t)b * S + s) * H + h) * D + tid] = (int8_t)q;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -690,6 +716,11 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     const int nq = (S + BM - 1) / BM;
     flb_prefill_attn_kernel<BN><<<(unsigned)(B * H * nq), NUM_THREADS, smem, stream>>>(tmQ, tmK, tmV, a);
     if (cudaGetLastError() != cudaSuccess) return FLB_ERR_LAUNCH;
+    if (p->out_q8) {
+        flb_attn_quant_transpose_kernel<<<dim3((unsigned)S, (unsigned)B), 128, 0, stream>>>((const float *)p->out, p->out_q8,
+                                                                                           p->out_q8_scale, H, S);
+        if (cudaGetLastError() != cudaSuccess) return FLB_ERR_LAUNCH;
+    }
     return FLB_OK;
 }
 

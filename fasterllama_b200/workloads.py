@@ -70,6 +70,7 @@ class Case:
             rope_pos0=self.rope_pos0, rope_add_past=self.rope_add_past, mask_mode=self.mask_mode,
             attn_mask=a.get("attn_mask"), softmax_scale=self.softmax_scale,
             scratch_zeroed=self.scratch_zeroed, split_len=self.split_len,
+            out_q8=a.get("out_q8"), out_q8_scale=a.get("out_q8_scale"),
         )
 
     def algorithmic_bytes(self) -> int:

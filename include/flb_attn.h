@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define FLB_ATTN_ABI_VERSION 1
+#define FLB_ATTN_ABI_VERSION 2
 
 /* ---- status codes (0 = ok, negative = error) ------------------------------------ */
 typedef enum flb_status {
@@ -137,6 +137,16 @@ typedef struct flb_attn_params {
     /* rows of one split-KV partition; 0 = default (512).  Results depend on this value
      * and on each sequence's own length only — never on B, H, the GPU count or the grid. */
     int split_len;
+
+    /* Optional fused epilogue (both NULL = off): the reference's next step,
+     * launchAttnQuantizedTransposeKernel (fasterLlama/cuda/decoder_kernels.cu:1179-1300, called at
+     * open_decoder.cu:245): per token row, absmax over ALL heads (floor -1e9f as there), scale =
+     * absmax / 127 into out_q8_scale[b*S+s], codes cvt.rni.sat.s8(x * 127.0f / absmax) into out_q8
+     * laid out [B, S, H*d].  Needs out_dtype == FLB_F32; `out` is still written.  Decode does it in
+     * the same launch (the last head to finish a sequence quantises its row); prefill adds one small
+     * kernel. */
+    int8_t *out_q8;
+    float *out_q8_scale;
 } flb_attn_params;
 
 /* ---- entry points --------------------------------------------------------------- */

@@ -17,6 +17,9 @@
  *   FLB_CACHE_F16=1   keep the caches in fp16 inside the caller's float slabs (first half of each slab)
  *   FLB_MASK_MODE=n   force a flb_mask_mode (default: the caller's additive mask is classified once
  *                     with flb_attn_classify_mask and the matching index-computed mode is used)
+ *   FLB_FUSE_QUANT=1  also do the step that follows attention (launchAttnQuantizedTransposeKernel,
+ *                     open_decoder.cu:245-246) inside the call; the caller then skips its own launch:
+ *                         if (!flb_open_decoder_fused_quant()) launchAttnQuantizedTransposeKernel(...);
  */
 #ifndef FLB_OPEN_DECODER_H
 #define FLB_OPEN_DECODER_H
@@ -35,13 +38,23 @@ static inline int flb_open_decoder_env_int(const char *name, int fallback) {
     return e ? atoi(e) : fallback;
 }
 
+static inline int flb_open_decoder_fused_quant(void) {
+    static int fused = -1;
+    if (fused < 0) fused = flb_open_decoder_env_int("FLB_FUSE_QUANT", 0);
+    return fused;
+}
+
+/* attn_q8 / attn_q8_scale: from_tensor_int8_buf_ / from_tensor_scale_buf_ (used when FLB_FUSE_QUANT=1; the scale
+ * buffer may be the same memory as from_tensor_scale_buf_ passed as the activation scale: every read of a row's
+ * activation scale happens before that row's new scale is written). */
 static inline void flb_open_decoder_attention(int batch_size_, int head_num_, int size_per_head_, int max_prompt_len_,
                                               int total_len_, int seq_len, int start_pos, const int32_t *query_buf_,
                                               const int32_t *key_buf_, const int32_t *value_buf_,
                                               const float *from_tensor_scale_buf_, const float *q_weight_scale,
                                               const float *k_weight_scale, const float *v_weight_scale, const float *freq_cis,
                                               const float *attn_mask, float *key_cache_, float *value_cache_,
-                                              float *query_out_buf_, float *qk_buf_, float *qkv_buf_, cudaStream_t stream) {
+                                              float *query_out_buf_, float *qk_buf_, float *qkv_buf_, int8_t *attn_q8,
+                                              float *attn_q8_scale, cudaStream_t stream) {
     static int cache_f16 = -1, mask_mode = -1;
     if (cache_f16 < 0) cache_f16 = flb_open_decoder_env_int("FLB_CACHE_F16", 0);
     if (mask_mode < 0) {
@@ -89,6 +102,10 @@ static inline void flb_open_decoder_attention(int batch_size_, int head_num_, in
     ap.scratch = query_out_buf_;
     ap.scratch_bytes = sizeof(float) * ((size_t)(qk_buf_ - query_out_buf_) + (size_t)batch_size_ * head_num_ * max_prompt_len_ * total_len_);
     ap.scratch_zeroed = 0;
+    if (flb_open_decoder_fused_quant()) {
+        ap.out_q8 = attn_q8;
+        ap.out_q8_scale = attn_q8_scale;
+    }
     const int st = flb_attn_forward(&ap, stream);
     if (st != FLB_OK) {
         printf("CUDA Error:\n    File:   %s\n    Line:   %d\n    flb_attn status: %d (%s)\n", __FILE__, __LINE__, st,

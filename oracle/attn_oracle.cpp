@@ -266,6 +266,28 @@ int orc_attention(const flb_attn_params *p, int flags) {
     return status;
 }
 
+// The step after attention: per token row, absmax over all heads, scale and int8 codes, transposed.
+// Restates warpAttnQuantizedTransposeKernel / blockAttnQuantizedTransposeKernel
+// (decoder_kernels.cu:1179-1255): absmax starts at -1e9f and ignores NaN (fmaxf), scale = absmax / 127,
+// code = round-to-nearest-even, saturated to [-128, 127], of x * 127.0f / absmax (cvt.rni.sat.s8.f32,
+// cuda_kernels.cuh:34-41; a NaN input converts to 0).  attn [B,H,S,d] fp32 -> q8 [B,S,H*d], scale [B*S].
+void orc_attn_quantize(const float *attn, int8_t *q8, float *scale, int B, int H, int S, int d) {
+    for (int b = 0; b < B; ++b)
+        for (int s = 0; s < S; ++s) {
+            float amax = -1e9f;
+            for (int h = 0; h < H; ++h)
+                for (int i = 0; i < d; ++i) amax = std::fmax(amax, std::fabs(attn[(((size_t)b * H + h) * S + s) * d + i]));
+            scale[(size_t)b * S + s] = amax / 127.0f;
+            for (int h = 0; h < H; ++h)
+                for (int i = 0; i < d; ++i) {
+                    const float x = attn[(((size_t)b * H + h) * S + s) * d + i] * 127.0f / amax;
+                    float r = std::nearbyint(x); // default rounding mode: to nearest, ties to even
+                    int q = std::isnan(r) ? 0 : (r > 127.f ? 127 : (r < -128.f ? -128 : (int)r));
+                    q8[(((size_t)b * S + s) * H + h) * d + i] = (int8_t)q;
+                }
+        }
+}
+
 // Thread control for the timed CPU baseline; returns the thread count that will be used.
 int orc_set_threads(int n) {
 #ifdef _OPENMP

@@ -118,10 +118,13 @@ def main():
     ap.add_argument("--out", required=True)
     ap.add_argument("--mask", default="inclusive", choices=["inclusive", "strict"])
     ap.add_argument("--cache-f16", action="store_true")
+    ap.add_argument("--fuse-quant", action="store_true", help="adaptor also does the attention-output quantisation")
     ap.add_argument("--repeat", type=int, default=1, help="runs; the time of the last one is reported")
     args = ap.parse_args()
     if args.cache_f16:
         os.environ["FLB_CACHE_F16"] = "1"
+    if args.fuse_quant:
+        os.environ["FLB_FUSE_QUANT"] = "1"
     cfg = CONFIGS[args.config]
     for _ in range(args.repeat):
         ids, sl, ms = run(args.variant, cfg, mask=args.mask)

@@ -70,6 +70,13 @@ def patch_gemv(src: str) -> None:
     open(p, "w").write(t)
 
 
+def patch_quant_call(text: str) -> str:
+    """The reference's own attention-output quantisation launch is skipped when the adaptor has done it."""
+    return _sub(text, r"(\n\s*)launchAttnQuantizedTransposeKernel\(from_tensor_int8_buf_, qkv_buf_,",
+                r"\1if (!flb_open_decoder_fused_quant()) launchAttnQuantizedTransposeKernel(from_tensor_int8_buf_, qkv_buf_,", 1,
+                "optional fused quantisation")
+
+
 def patch_adaptor(src: str) -> None:
     p = os.path.join(src, "cuda", "open_decoder.cu")
     lines = open(p).read().split("\n")
@@ -78,9 +85,9 @@ def patch_adaptor(src: str) -> None:
                                        query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
                                        param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
                                        param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
-                                       key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, param_.stream);"""
+                                       key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, from_tensor_int8_buf_, from_tensor_scale_buf_, param_.stream);"""
     lines[s:e] = call.split("\n")
-    text = "\n".join(lines)
+    text = patch_quant_call("\n".join(lines))
     text = text.replace('#include "open_decoder.h"', '#include "open_decoder.h"\n#include "flb_open_decoder.h"', 1)
     open(p, "w").write(text)
 
@@ -99,7 +106,7 @@ def patch_mix(src: str) -> None:
                                        query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
                                        param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
                                        param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
-                                       key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, param_.stream);
+                                       key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, from_tensor_int8_buf_, from_tensor_scale_buf_, param_.stream);
             } else {"""
     tail = """            }
             if ((flb_use & 4) && seq_len == 1) {
@@ -113,7 +120,7 @@ def patch_mix(src: str) -> None:
                                        query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
                                        param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
                                        param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
-                                       key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, param_.stream);
+                                       key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, from_tensor_int8_buf_, from_tensor_scale_buf_, param_.stream);
                 cudaStreamSynchronize(param_.stream);
                 cudaMemcpy(h_flb.data(), qkv_buf_, n * sizeof(float), cudaMemcpyDeviceToHost);
                 cudaMemcpy(qkv_buf_, h_ref.data(), n * sizeof(float), cudaMemcpyHostToDevice);

@@ -35,6 +35,7 @@ def load():
         lib.orc_rope_row.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         lib.orc_softmax_row.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.POINTER(C.c_int)]
         lib.orc_freq_cis.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_double]
+        lib.orc_attn_quantize.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]
         _lib = lib
     return _lib
 
@@ -76,3 +77,14 @@ def freq_cis(rows: int, d: int = 128, base: float = 10000.0) -> np.ndarray:
     t = np.empty((rows, d), dtype=np.float32)
     load().orc_freq_cis(t.ctypes.data, rows, d, float(base))
     return t
+
+
+def attn_quantize(attn: np.ndarray):
+    """The reference's attention-output quantisation on the host: attn [B,H,S,d] fp32 ->
+    (codes int8 [B,S,H*d], scale fp32 [B*S])."""
+    a = np.ascontiguousarray(attn, dtype=np.float32)
+    B, H, S, d = a.shape
+    q8 = np.empty((B, S, H * d), dtype=np.int8)
+    sc = np.empty((B * S,), dtype=np.float32)
+    load().orc_attn_quantize(a.ctypes.data, q8.ctypes.data, sc.ctypes.data, B, H, S, d)
+    return q8, sc

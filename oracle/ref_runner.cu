@@ -91,6 +91,15 @@ int ref_attention(void *handle, const ref_attn_args *a, void *cuda_stream) {
     return ce == cudaSuccess ? 0 : 2000 + (int)ce;
 }
 
+// The reference's attention-output quantisation + transpose (fasterLlama/cuda/decoder_kernels.cu:1179-1300).
+int ref_attn_quant(int8_t *attn_buf, const float *attn, float *scale, int batch_size, int head_num, int seq_len,
+                   int size_per_head, void *cuda_stream) {
+    FasterLLaMA::launchAttnQuantizedTransposeKernel(attn_buf, attn, scale, batch_size, head_num, seq_len, size_per_head,
+                                                    static_cast<cudaStream_t>(cuda_stream));
+    const cudaError_t ce = cudaGetLastError();
+    return ce == cudaSuccess ? 0 : 2000 + (int)ce;
+}
+
 // The reference's RoPE table generator (fasterLlama/cuda/decoding_kernels.cu:85-135).
 int ref_freq_cis(float *freq_cis, int size_per_head, int rows, void *cuda_stream) {
     FasterLLaMA::launchPrecomputeFreqsCis(freq_cis, size_per_head, rows, static_cast<cudaStream_t>(cuda_stream));

@@ -45,6 +45,9 @@ class RefRunner:
         self.lib.ref_attention.argtypes = [C.c_void_p, C.POINTER(RefAttnArgs), C.c_void_p]
         self.lib.ref_freq_cis.restype = C.c_int
         self.lib.ref_freq_cis.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        if hasattr(self.lib, "ref_attn_quant"):
+            self.lib.ref_attn_quant.restype = C.c_int
+            self.lib.ref_attn_quant.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
         self.handle = self.lib.ref_create()
         if not self.handle:
             raise RuntimeError("cublasCreate failed")
@@ -93,6 +96,18 @@ class RefRunner:
 
         s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
         return int(self.lib.ref_attention(self.handle, C.byref(args), s))
+
+    def attn_quant(self, attn):
+        """The reference's launchAttnQuantizedTransposeKernel on a [B,H,S,d] fp32 CUDA tensor."""
+        import torch
+
+        B, H, S, d = attn.shape
+        q8 = torch.empty((B, S, H * d), dtype=torch.int8, device=attn.device)
+        sc = torch.empty((B * S,), dtype=torch.float32, device=attn.device)
+        st = self.lib.ref_attn_quant(q8.data_ptr(), attn.data_ptr(), sc.data_ptr(), B, H, S, d, torch.cuda.current_stream().cuda_stream)
+        if st != 0:
+            raise RuntimeError(f"ref_attn_quant status {st}")
+        return q8, sc
 
     def freq_cis(self, rows: int, d: int = 128):
         import torch

@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.EXPORTS), (declared ^ set(_lib.EXPORTS))
     for name in declared:
         assert hasattr(lib, name)
-    assert lib.flb_attn_abi_version() == 1
+    assert lib.flb_attn_abi_version() == 2
 
 
 def test_missing_library_fails_loudly(tmp_path):
@@ -39,11 +39,11 @@ def test_struct_layout_matches_the_header():
     exe = os.path.join(tmp, "abi_probe")
     with open(probe, "w") as f:
         f.write('#include <stdio.h>\n#include "flb_attn.h"\nint main(void){printf("%zu %zu %zu %zu\\n", sizeof(flb_attn_params),'
-                ' offsetof(flb_attn_params, past_lens), offsetof(flb_attn_params, softmax_scale), offsetof(flb_attn_params, split_len));return 0;}\n')
+                ' offsetof(flb_attn_params, past_lens), offsetof(flb_attn_params, softmax_scale), offsetof(flb_attn_params, out_q8_scale));return 0;}\n')
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), probe, "-o", exe], check=True)
     got = [int(x) for x in subprocess.run([exe], check=True, capture_output=True, text=True).stdout.split()]
     P = _lib.FlbAttnParams
-    assert got == [C.sizeof(P), P.past_lens.offset, P.softmax_scale.offset, P.split_len.offset]
+    assert got == [C.sizeof(P), P.past_lens.offset, P.softmax_scale.offset, P.out_q8_scale.offset]
 
 
 def _valid_case():
