@@ -47,14 +47,14 @@ static inline int flb_open_decoder_fused_quant(void) {
 /* attn_q8 / attn_q8_scale: from_tensor_int8_buf_ / from_tensor_scale_buf_ (used when FLB_FUSE_QUANT=1; the scale
  * buffer may be the same memory as from_tensor_scale_buf_ passed as the activation scale: every read of a row's
  * activation scale happens before that row's new scale is written). */
-static inline void flb_open_decoder_attention(int batch_size_, int head_num_, int size_per_head_, int max_prompt_len_,
-                                              int total_len_, int seq_len, int start_pos, const int32_t *query_buf_,
-                                              const int32_t *key_buf_, const int32_t *value_buf_,
-                                              const float *from_tensor_scale_buf_, const float *q_weight_scale,
-                                              const float *k_weight_scale, const float *v_weight_scale, const float *freq_cis,
-                                              const float *attn_mask, float *key_cache_, float *value_cache_,
-                                              float *query_out_buf_, float *qk_buf_, float *qkv_buf_, int8_t *attn_q8,
-                                              float *attn_q8_scale, cudaStream_t stream) {
+static inline void flb_open_decoder_attention_core(int batch_size_, int head_num_, int size_per_head_, int total_len_,
+                                                   int seq_len, int start_pos, const int32_t *query_buf_,
+                                                   const int32_t *key_buf_, const int32_t *value_buf_,
+                                                   const float *from_tensor_scale_buf_, const float *q_weight_scale,
+                                                   const float *k_weight_scale, const float *v_weight_scale,
+                                                   const float *freq_cis, const float *attn_mask, float *key_cache_,
+                                                   float *value_cache_, void *scratch, size_t scratch_bytes, float *out,
+                                                   int8_t *attn_q8, float *attn_q8_scale, cudaStream_t stream) {
     static int cache_f16 = -1, mask_mode = -1;
     if (cache_f16 < 0) cache_f16 = flb_open_decoder_env_int("FLB_CACHE_F16", 0);
     if (mask_mode < 0) {
@@ -65,7 +65,7 @@ static inline void flb_open_decoder_attention(int batch_size_, int head_num_, in
             } else {
                 // one look at the caller's mask, at the first call only (synchronises the stream once)
                 int m = FLB_MASK_GENERIC;
-                if (flb_attn_classify_mask(attn_mask, total_len_, total_len_, qk_buf_, &m, stream) != FLB_OK) m = FLB_MASK_GENERIC;
+                if (flb_attn_classify_mask(attn_mask, total_len_, total_len_, scratch, &m, stream) != FLB_OK) m = FLB_MASK_GENERIC;
                 mask_mode = m;
             }
         }
@@ -95,12 +95,11 @@ static inline void flb_open_decoder_attention(int batch_size_, int head_num_, in
     ap.k_cache = key_cache_;
     ap.v_cache = value_cache_;
     ap.cache_dtype = cache_f16 ? FLB_F16 : FLB_F32;
-    ap.out = qkv_buf_;
+    ap.out = out;
     ap.out_dtype = FLB_F32;
     ap.softmax_scale = 1.0f / sqrtf((float)size_per_head_);
-    /* query_out_buf_ .. end of qk_buf_: 3 * buf_size floats + the score buffer, contiguous */
-    ap.scratch = query_out_buf_;
-    ap.scratch_bytes = sizeof(float) * ((size_t)(qk_buf_ - query_out_buf_) + (size_t)batch_size_ * head_num_ * max_prompt_len_ * total_len_);
+    ap.scratch = scratch;
+    ap.scratch_bytes = scratch_bytes;
     ap.scratch_zeroed = 0;
     if (flb_open_decoder_fused_quant()) {
         ap.out_q8 = attn_q8;
@@ -113,5 +112,87 @@ static inline void flb_open_decoder_attention(int batch_size_, int head_num_, in
         exit(1);
     }
 }
+
+/* The call OpenDecoder::forward makes: scratch = query_out_buf_ .. end of qk_buf_ (3 * buf_size floats + the score
+ * buffer, contiguous), output = qkv_buf_. */
+static inline void flb_open_decoder_attention(int batch_size_, int head_num_, int size_per_head_, int max_prompt_len_,
+                                              int total_len_, int seq_len, int start_pos, const int32_t *query_buf_,
+                                              const int32_t *key_buf_, const int32_t *value_buf_,
+                                              const float *from_tensor_scale_buf_, const float *q_weight_scale,
+                                              const float *k_weight_scale, const float *v_weight_scale, const float *freq_cis,
+                                              const float *attn_mask, float *key_cache_, float *value_cache_,
+                                              float *query_out_buf_, float *qk_buf_, float *qkv_buf_, int8_t *attn_q8,
+                                              float *attn_q8_scale, cudaStream_t stream) {
+    const size_t bytes =
+        sizeof(float) * ((size_t)(qk_buf_ - query_out_buf_) + (size_t)batch_size_ * head_num_ * max_prompt_len_ * total_len_);
+    flb_open_decoder_attention_core(batch_size_, head_num_, size_per_head_, total_len_, seq_len, start_pos, query_buf_, key_buf_,
+                                    value_buf_, from_tensor_scale_buf_, q_weight_scale, k_weight_scale, v_weight_scale, freq_cis,
+                                    attn_mask, key_cache_, value_cache_, query_out_buf_, bytes, qkv_buf_, attn_q8, attn_q8_scale,
+                                    stream);
+}
+
+/* ---- tensor-parallel form (compiled only with -DFLB_WITH_NCCL) -------------------------------------
+ * Each rank owns head_num/size heads: its OpenDecoder::forward computes the Q/K/V projections for its
+ * column slice of the weights only (pointer offset rank*hidden/size, leading dimension unchanged),
+ * calls flb_open_decoder_attention_tp() on those heads against its own cache shard (the first 1/size of
+ * every layer's slab), and gets the full [B,H,S,d] attention output back through ONE exchange: an
+ * all-gather of the fp32 head outputs (the next kernel needs the absmax over all heads of a token row).
+ * Everything after that stays replicated.  Exactly one translation unit defines
+ * FLB_OPEN_DECODER_TP_STATE before including this header; it holds the communicator. */
+#ifdef FLB_WITH_NCCL
+#include <nccl.h>
+
+typedef struct flb_tp_state_t {
+    ncclComm_t comm;
+    int rank, size;
+} flb_tp_state_t;
+#ifdef FLB_OPEN_DECODER_TP_STATE
+flb_tp_state_t flb_tp_state = {0, 0, 1};
+#else
+extern flb_tp_state_t flb_tp_state;
+#endif
+
+static inline int flb_tp_size(void) { return flb_tp_state.size; }
+static inline int flb_tp_rank(void) { return flb_tp_state.rank; }
+
+static inline void flb_open_decoder_attention_tp(int batch_size_, int head_num_, int size_per_head_, int max_prompt_len_,
+                                                 int total_len_, int seq_len, int start_pos, const int32_t *query_buf_,
+                                                 const int32_t *key_buf_, const int32_t *value_buf_,
+                                                 const float *from_tensor_scale_buf_, const float *q_weight_scale,
+                                                 const float *k_weight_scale, const float *v_weight_scale,
+                                                 const float *freq_cis, const float *attn_mask, float *key_cache_,
+                                                 float *value_cache_, float *query_out_buf_, float *qk_buf_, float *qkv_buf_,
+                                                 cudaStream_t stream) {
+    const int g = flb_tp_state.size, r = flb_tp_state.rank;
+    const int h_local = head_num_ / g;
+    const size_t col0 = (size_t)r * h_local * size_per_head_;
+    if (g == 1) {
+        flb_open_decoder_attention(batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos, query_buf_,
+                                   key_buf_, value_buf_, from_tensor_scale_buf_, q_weight_scale, k_weight_scale, v_weight_scale,
+                                   freq_cis, attn_mask, key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, NULL, NULL, stream);
+        (void)max_prompt_len_;
+        return;
+    }
+    /* local heads: q/k/v are [B*S, h_local*d].  query_out_buf_, key_out_buf_, value_out_fp_buf_ are three equal
+     * buffers of B*P*hidden floats in front of qk_buf_: the first two are the scratch, the third takes the local
+     * output [B,h_local,S,d] (at most half of it with two ranks or more). */
+    const size_t buf_size = (size_t)(qk_buf_ - query_out_buf_) / 3;
+    float *local_out = query_out_buf_ + 2 * buf_size;
+    flb_open_decoder_attention_core(batch_size_, h_local, size_per_head_, total_len_, seq_len, start_pos, query_buf_, key_buf_,
+                                    value_buf_, from_tensor_scale_buf_, q_weight_scale + col0, k_weight_scale + col0,
+                                    v_weight_scale + col0, freq_cis, attn_mask, key_cache_, value_cache_, query_out_buf_,
+                                    sizeof(float) * 2 * buf_size, local_out, NULL, NULL, stream);
+    /* one all-gather of head outputs: per sequence, every rank's [h_local, S, d] block lands in head order */
+    const size_t blk = (size_t)h_local * seq_len * size_per_head_;
+    ncclGroupStart();
+    for (int b = 0; b < batch_size_; ++b)
+        ncclAllGather(local_out + (size_t)b * blk, qkv_buf_ + (size_t)b * blk * g, blk, ncclFloat, flb_tp_state.comm, stream);
+    const ncclResult_t nr = ncclGroupEnd();
+    if (nr != ncclSuccess) {
+        printf("NCCL Error:\n    File:   %s\n    Line:   %d\n    %s\n", __FILE__, __LINE__, ncclGetErrorString(nr));
+        exit(1);
+    }
+}
+#endif /* FLB_WITH_NCCL */
 
 #endif /* FLB_OPEN_DECODER_H */

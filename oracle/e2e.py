@@ -48,10 +48,41 @@ def quantise(w: torch.Tensor):
     return q.contiguous(), scale.float().contiguous()
 
 
+_LIBS: dict = {}
+
+
+def load(variant: str):
+    if variant not in _LIBS:
+        lib = C.CDLL(os.path.join(HERE, "_ref", f"libe2e_{variant}.so"))
+        lib.e2e_run.restype = C.c_int
+        lib.e2e_run.argtypes = [C.POINTER(Args), C.POINTER(C.c_float)]
+        _LIBS[variant] = lib
+    return _LIBS[variant]
+
+
+def tp_init(variant: str):
+    """Under torchrun with the `tp` library: rank 0 makes an NCCL id, every rank joins the communicator the
+    patched OpenDecoder::forward uses for its one all-gather per layer.  Returns (rank, world, local_rank)."""
+    rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0")))
+    if variant != "tp" or world == 1:
+        return rank, world, local
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local)
+    dist.init_process_group("gloo")
+    lib = load(variant)
+    buf = C.create_string_buffer(128)
+    if rank == 0:
+        assert lib.e2e_tp_unique_id(buf) == 0
+    box = [bytes(buf.raw)]
+    dist.broadcast_object_list(box, src=0)
+    lib.e2e_tp_init.argtypes = [C.c_int, C.c_int, C.c_int, C.c_char_p]
+    assert lib.e2e_tp_init(rank, world, local, box[0]) == 0, "ncclCommInitRank failed"
+    return rank, world, local
+
+
 def run(variant: str, cfg: dict, mask: str = "inclusive", device: int = 0):
-    lib = C.CDLL(os.path.join(HERE, "_ref", f"libe2e_{variant}.so"))
-    lib.e2e_run.restype = C.c_int
-    lib.e2e_run.argtypes = [C.POINTER(Args), C.POINTER(C.c_float)]
+    lib = load(variant)
     dev = f"cuda:{device}"
     g = torch.Generator(device=dev)
     g.manual_seed(cfg["seed"])
@@ -113,7 +144,7 @@ def run(variant: str, cfg: dict, mask: str = "inclusive", device: int = 0):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--variant", required=True, choices=["ref", "flb", "ref32", "mix"])
+    ap.add_argument("--variant", required=True, choices=["ref", "flb", "ref32", "mix", "tp"])
     ap.add_argument("--config", default="small", choices=sorted(CONFIGS))
     ap.add_argument("--out", required=True)
     ap.add_argument("--mask", default="inclusive", choices=["inclusive", "strict"])
@@ -126,11 +157,21 @@ def main():
     if args.fuse_quant:
         os.environ["FLB_FUSE_QUANT"] = "1"
     cfg = CONFIGS[args.config]
+    rank, world, local = tp_init(args.variant)
     for _ in range(args.repeat):
-        ids, sl, ms = run(args.variant, cfg, mask=args.mask)
+        ids, sl, ms = run(args.variant, cfg, mask=args.mask, device=local)
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # the slowest rank's time
+        ms = float(t.item())
+        dist.barrier()
+    if rank != 0:
+        return
     np.savez(args.out, ids=ids, seq_len=sl, ms=ms)
     toks = cfg["batch"] * cfg["max_gen_len"]
-    print(json.dumps({"variant": args.variant, "config": args.config, "mask": args.mask, "cache_f16": bool(args.cache_f16),
+    print(json.dumps({"variant": args.variant, "tp": world, "config": args.config, "mask": args.mask, "cache_f16": bool(args.cache_f16),
                       "ms": round(ms, 2), "tokens_per_s": round(toks / ms * 1e3, 1), "first_ids": ids[0, :8].tolist(),
                       "seq_len": sl[:4].tolist()}))
 

@@ -9,8 +9,13 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "decoding_sampling.h"
+#ifdef FLB_WITH_NCCL
+#define FLB_OPEN_DECODER_TP_STATE
+#include "flb_open_decoder.h"
+#endif
 
 extern "C" {
 
@@ -40,6 +45,27 @@ typedef struct e2e_args {
     int *output_ids;        // [B, T]
     int *seq_len;           // [B]
 } e2e_args;
+
+#ifdef FLB_WITH_NCCL
+// tensor-parallel set-up: rank 0 makes the id, the caller broadcasts its 128 bytes, every rank joins
+int e2e_tp_unique_id(char *out128) {
+    ncclUniqueId id;
+    if (ncclGetUniqueId(&id) != ncclSuccess) return 1;
+    memcpy(out128, &id, sizeof(id));
+    return 0;
+}
+int e2e_tp_init(int rank, int size, int device, const char *id128) {
+    cudaSetDevice(device);
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    ncclComm_t comm;
+    if (ncclCommInitRank(&comm, size, id, rank) != ncclSuccess) return 1;
+    flb_tp_state.comm = comm;
+    flb_tp_state.rank = rank;
+    flb_tp_state.size = size;
+    return 0;
+}
+#endif
 
 // returns 0; *ms = time of DecodingSampling::forward between two events on its stream
 int e2e_run(const e2e_args *a, float *ms) {

@@ -10,6 +10,8 @@ reference is committed here; the copy lives under oracle/_ref/, which is git-ign
         (the whole attention section) replaced by one call of flb_open_decoder_attention()
         (include/flb_open_decoder.h) — the drop-in adaptor.
 
+  oracle/_ref/libe2e_tp.so    the tensor-parallel layer: like libe2e_flb.so, plus the Q/K/V GEMMs restricted to the rank's
+        column slice of the weights and flb_open_decoder_attention_tp() (head-sharded attention + one NCCL all-gather).
   oracle/_ref/libe2e_ref32.so like libe2e_ref.so, but with the prefill GEMMs computing in true fp32
         (CUBLAS_COMPUTE_32F instead of CUBLAS_COMPUTE_32F_FAST_16F in common.h) — used only to measure how far
         the reference's own fp16 tensor-core rounding moves its sampled tokens.
@@ -136,6 +138,37 @@ def patch_mix(src: str) -> None:
     open(p, "w").write(text)
 
 
+def patch_tp(src: str) -> None:
+    """Tensor-parallel layer: Q/K/V projections on this rank's column slice of the weights, attention on its heads
+    through flb_open_decoder_attention_tp (which all-gathers the head outputs); the rest of the layer is untouched."""
+    p = os.path.join(src, "cuda", "open_decoder.cu")
+    text = open(p).read()
+    text = _sub(text, r"(int k = hidden_units_;\n)", r"\1            const int n_tp = n / flb_tp_size();\n            const int tp_col0 = flb_tp_rank() * n_tp;\n", 1, "tp slice")
+    for x in ("query", "key", "value"):
+        text = _sub(text,
+                    rf"n, m, k,(\s*)&weight_alpha,(\s*)param_\.attention\.{x}_weight\.kernel, weight_Traits_::AType, n,(\s*)from_tensor_int8_buf_, weight_Traits_::BType, k,(\s*)&weight_beta,(\s*){x}_buf_, weight_Traits_::CType, n,",
+                    rf"n_tp, m, k,\1&weight_alpha,\2param_.attention.{x}_weight.kernel + tp_col0, weight_Traits_::AType, n,\3from_tensor_int8_buf_, weight_Traits_::BType, k,\4&weight_beta,\5{x}_buf_, weight_Traits_::CType, n_tp,",
+                    1, f"{x} projection slice")
+    lines = text.split("\n")
+    s, e = None, None
+    for i, l in enumerate(lines):
+        if "Quantized-rope" in l and s is None:
+            s = i - 1
+        if "quantized qkv to int8" in l:
+            e = i - 2
+    if s is None or e is None or lines[s].strip() != "/**" or lines[e - 1].strip() != "}":
+        raise RuntimeError("attention section anchors not found")
+    call = """            flb_open_decoder_attention_tp(batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
+                                          query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
+                                          param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
+                                          param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
+                                          key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, param_.stream);"""
+    lines[s:e] = call.split("\n")
+    text = "\n".join(lines)
+    text = text.replace('#include "open_decoder.h"', '#include "open_decoder.h"\n#include "flb_open_decoder.h"', 1)
+    open(p, "w").write(text)
+
+
 def build(name: str, ref_root: str) -> str:
     vdir = os.path.join(OUT, "variants", name)
     if os.path.isdir(vdir):
@@ -151,6 +184,8 @@ def build(name: str, ref_root: str) -> str:
         patch_gemv(src)
     elif name == "mix":
         patch_mix(src)
+    elif name == "tp":
+        patch_tp(src)
     else:
         patch_adaptor(src)
     if name == "ref32":
@@ -163,16 +198,20 @@ def build(name: str, ref_root: str) -> str:
     cmd = ["nvcc", "-std=c++17", "-O3", "-DNDEBUG", "-w", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
            "-shared", "-cudart", "shared", "-I", src, "-I", os.path.join(src, "cuda"), "-I", os.path.join(ROOT, "include"),
            *cu, os.path.join(HERE, "e2e_runner.cu"), "-lcublas", "-lcurand", "-o", lib]
-    if name in ("flb", "mix"):
+    if name in ("flb", "mix", "tp"):
         pkg = os.path.join(ROOT, "fasterllama_b200")
         cmd += ["-L", pkg, "-lflb_attn", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../fasterllama_b200"]
+    if name == "tp":
+        import torch  # the NCCL this process will already have loaded: link against the same library
+        nccl_dir = os.path.join(os.path.dirname(os.path.dirname(torch.__file__)), "nvidia", "nccl")
+        cmd += ["-DFLB_WITH_NCCL", "-I", os.path.join(nccl_dir, "include"), "-L", os.path.join(nccl_dir, "lib"), "-l:libnccl.so.2"]
     subprocess.run(cmd, check=True)
     return lib
 
 
 def main(ref_root: str = "/root/reference") -> None:
     os.makedirs(OUT, exist_ok=True)
-    for name in (sys.argv[2:] or ["ref", "flb", "ref32"]):
+    for name in (sys.argv[2:] or ["ref", "flb", "ref32", "mix", "tp"]):
         print("built", build(name, ref_root))
 
 

@@ -70,3 +70,34 @@ def test_head_sharded_layer_on_two_gpus(cuda_device):
         p.join(timeout=300)
         assert p.exitcode == 0
     assert ret.get(timeout=10)
+
+
+E2E_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.skipif(not all(os.path.exists(os.path.join(E2E_DIR, f"libe2e_{v}.so")) for v in ("flb", "tp")),
+                    reason="end-to-end libraries not built")
+@pytest.mark.parametrize("config", ["small", "medium"])
+def test_tensor_parallel_generation_matches_one_gpu(cuda_device, tmp_path, config):
+    """The reference's DecodingSampling with the tensor-parallel layer (Q/K/V projections on a column slice,
+    head-sharded attention, one NCCL all-gather of head outputs per layer) on two GPUs samples exactly the
+    ids of the one-GPU adaptor run: int32 projections are exact under the column split, each head's
+    attention is bit-identical wherever it runs, and the gather is a copy."""
+    import subprocess
+
+    root = os.path.dirname(E2E_DIR.rstrip("/"))
+    e2e = os.path.join(root, "e2e.py")
+    one, two = str(tmp_path / "one.npz"), str(tmp_path / "two.npz")
+    r = subprocess.run([sys.executable, e2e, "--variant", "flb", "--config", config, "--out", one], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-1500:]
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", str(port), e2e, "--variant", "tp", "--config", config, "--out", two],
+                       capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    a, b = np.load(one), np.load(two)
+    assert np.array_equal(a["seq_len"], b["seq_len"])
+    assert np.array_equal(a["ids"], b["ids"])
