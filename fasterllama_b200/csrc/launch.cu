@@ -215,8 +215,8 @@ int flb_attn_scratch_status(const void *scratch, unsigned *status_out, void *cud
 // ---- mask classification ---------------------------------------------------------------------
 namespace {
 
-// verdict bits: 1 = consistent with strict causal, 2 = with inclusive causal, 4 = all zero
-__global__ void classify_mask_kernel(const float *__restrict__ mask, int rows, int stride, unsigned *verdict) {
+// maskbits bits: 1 = consistent with strict causal, 2 = with inclusive causal, 4 = all zero
+__global__ void classify_mask_kernel(const float *__restrict__ mask, int rows, int stride, unsigned *maskbits) {
     unsigned bad = 0;
     const size_t n = (size_t)rows * rows;
     for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
@@ -228,7 +228,7 @@ __global__ void classify_mask_kernel(const float *__restrict__ mask, int rows, i
         if (!((c < r) ? keep : drop)) bad |= 1u;
         if (!((c <= r) ? keep : drop)) bad |= 2u;
     }
-    if (bad) atomicAnd(verdict, ~bad);
+    if (bad) atomicAnd(maskbits, ~bad);
 }
 
 } // namespace
@@ -238,15 +238,15 @@ extern "C" int flb_attn_classify_mask(const float *attn_mask, int rows, int row_
     if (!attn_mask || !mode_out || !scratch16) return FLB_ERR_NULL_POINTER;
     if (rows <= 0 || row_stride < rows) return FLB_ERR_BAD_SHAPE;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-    unsigned *verdict = static_cast<unsigned *>(scratch16);
+    unsigned *maskbits = static_cast<unsigned *>(scratch16);
     const unsigned all = 7u;
-    if (cudaMemcpyAsync(verdict, &all, sizeof(all), cudaMemcpyHostToDevice, stream) != cudaSuccess) return FLB_ERR_LAUNCH;
+    if (cudaMemcpyAsync(maskbits, &all, sizeof(all), cudaMemcpyHostToDevice, stream) != cudaSuccess) return FLB_ERR_LAUNCH;
     const size_t n = (size_t)rows * rows;
     const unsigned blocks = (unsigned)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
-    classify_mask_kernel<<<blocks, 256, 0, stream>>>(attn_mask, rows, row_stride, verdict);
+    classify_mask_kernel<<<blocks, 256, 0, stream>>>(attn_mask, rows, row_stride, maskbits);
     if (cudaGetLastError() != cudaSuccess) return FLB_ERR_LAUNCH;
     unsigned v = 0;
-    if (cudaMemcpyAsync(&v, verdict, sizeof(v), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return FLB_ERR_LAUNCH;
+    if (cudaMemcpyAsync(&v, maskbits, sizeof(v), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return FLB_ERR_LAUNCH;
     if (cudaStreamSynchronize(stream) != cudaSuccess) return FLB_ERR_LAUNCH;
     if (v & 4u)
         *mode_out = FLB_MASK_NONE;

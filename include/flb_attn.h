@@ -184,7 +184,7 @@ int flb_attn_forward(const flb_attn_params *p, void *cuda_stream);
  * A masked entry counts as such only when it is <= -1e30 (the samples use -FLT_MAX), because a
  * milder value such as -1e5 does not drop a key when the whole row is masked.
  * `scratch16` is 16 bytes of device memory the check may overwrite.  Synchronises the stream
- * (it copies the verdict to the host): call it once at set-up, never per step. */
+ * (it copies the answer to the host): call it once at set-up, never per step. */
 int flb_attn_classify_mask(const float *attn_mask, int rows, int row_stride, void *scratch16,
                            int *mode_out, void *cuda_stream);
 

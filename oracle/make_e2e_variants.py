@@ -59,7 +59,7 @@ def attention_section(lines: list[str]) -> tuple[int, int]:
     """0-based [start, end) of open_decoder.cu:138-239, checked against its anchors."""
     start, end = 137, 239
     if "Quantized-rope" not in lines[start + 1] or lines[end - 1].strip() != "}" or "quantized qkv to int8" not in lines[end + 2]:
-        raise RuntimeError("open_decoder.cu does not look like the surveyed revision (attention section anchors moved)")
+        raise RuntimeError("open_decoder.cu does not look like the expected revision (attention section anchors moved)")
     return start, end
 
 
@@ -206,6 +206,8 @@ def build(name: str, ref_root: str) -> str:
         nccl_dir = os.path.join(os.path.dirname(os.path.dirname(torch.__file__)), "nvidia", "nccl")
         cmd += ["-DFLB_WITH_NCCL", "-I", os.path.join(nccl_dir, "include"), "-L", os.path.join(nccl_dir, "lib"), "-l:libnccl.so.2"]
     subprocess.run(cmd, check=True)
+    if not os.environ.get("FLB_KEEP_VARIANT_SOURCES"):
+        shutil.rmtree(vdir)  # the patched copy of the reference's sources is only needed for the compile
     return lib
 
 

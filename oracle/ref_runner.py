@@ -66,15 +66,15 @@ class RefRunner:
         B, S, H, d = t["q"].shape
         T = t["k_cache"].shape[2]
         L = S + start_pos
-        if "_work" not in t:
+        if "_buffers" not in t:
             dev = t["q"].device
-            t["_work"] = {
+            t["_buffers"] = {
                 "q_out": torch.empty(B * H * S * d, dtype=torch.float32, device=dev),
                 "k_out": torch.empty(B * H * S * d, dtype=torch.float32, device=dev),
                 "v_out": torch.empty(B * H * S * d, dtype=torch.float32, device=dev),
                 "qk_buf": torch.zeros(B * H * S * max(T, d), dtype=torch.float32, device=dev),
             }
-        w = t["_work"]
+        w = t["_buffers"]
         a = RefAttnArgs()
         a.batch_size, a.head_num, a.size_per_head, a.seq_len, a.start_pos, a.total_len = B, H, d, S, start_pos, T
         a.Q, a.K, a.V = t["q"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr()

@@ -30,13 +30,11 @@ def test_missing_library_fails_loudly(tmp_path):
         _lib.load_library(str(tmp_path / "nope.so"))
 
 
-def test_struct_layout_matches_the_header():
+def test_struct_layout_matches_the_header(tmp_path):
     # a C compiler's view of the struct: compile a tiny probe against the header
     import subprocess
-    src = tmp = os.path.join(ROOT, "_work")
-    os.makedirs(tmp, exist_ok=True)
-    probe = os.path.join(tmp, "abi_probe.c")
-    exe = os.path.join(tmp, "abi_probe")
+    probe = str(tmp_path / "abi_probe.c")
+    exe = str(tmp_path / "abi_probe")
     with open(probe, "w") as f:
         f.write('#include <stdio.h>\n#include "flb_attn.h"\nint main(void){printf("%zu %zu %zu %zu\\n", sizeof(flb_attn_params),'
                 ' offsetof(flb_attn_params, past_lens), offsetof(flb_attn_params, softmax_scale), offsetof(flb_attn_params, out_q8_scale));return 0;}\n')
