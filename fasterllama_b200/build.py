@@ -74,10 +74,31 @@ def build_reference(force: bool = False) -> str | None:
     return out
 
 
+E2E_VARIANTS = ("ref", "flb", "ref32", "mix", "tp")
+
+
+def build_e2e_variants(force: bool = False) -> list[str]:
+    """End-to-end libraries around the reference's own DecodingSampling/OpenDecoder classes (test and baseline
+    infrastructure, oracle/make_e2e_variants.py).  Built only where the reference checkout exists; stale ones are
+    rebuilt when the runner, the patch script or the binding headers changed."""
+    ref_root = os.environ.get("FLB_REFERENCE_ROOT", "/root/reference")
+    out_dir = os.path.join(ORACLE_DIR, "_ref")
+    libs = [os.path.join(out_dir, f"libe2e_{v}.so") for v in E2E_VARIANTS]
+    if not os.path.isdir(ref_root):
+        return [l for l in libs if os.path.exists(l)]
+    deps = [os.path.join(ORACLE_DIR, "e2e_runner.cu"), os.path.join(ORACLE_DIR, "make_e2e_variants.py"),
+            os.path.join(ROOT, "include", "flb_open_decoder.h"), os.path.join(ROOT, "include", "flb_attn.h")]
+    stale = [v for v, l in zip(E2E_VARIANTS, libs) if force or not _newer(l, deps)]
+    if stale:
+        subprocess.run([sys.executable, os.path.join(ORACLE_DIR, "make_e2e_variants.py"), ref_root, *stale], check=True)
+    return libs
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_cuda(force, verbose)
     build_oracle(force)
     build_reference(force)
+    build_e2e_variants(force)
 
 
 if __name__ == "__main__":
