@@ -100,12 +100,15 @@ int flb_attn_validate(const flb_attn_params *p) {
         if (p->mask_mode == FLB_MASK_GENERIC && p->mask_row_stride < mp + 1) return FLB_ERR_BAD_SHAPE;
         if (!p->scratch) return FLB_ERR_NULL_POINTER;
         if (!aligned16(p->scratch)) return FLB_ERR_MISALIGNED;
-        const ScratchLayout l = layout_for(p->batch_size, p->head_num, nsplit_for(mp, split_len_of(p)));
+        const int nsm = nsplit_for(mp, split_len_of(p));
+        if ((unsigned long long)p->batch_size * p->head_num * nsm > 0x7fffffffull) return FLB_ERR_TOO_LARGE; // grid / int indices
+        const ScratchLayout l = layout_for(p->batch_size, p->head_num, nsm);
         if (p->scratch_bytes < l.total) return FLB_ERR_SCRATCH_TOO_SMALL;
     } else {
         // the reference's prefill attends over the fresh rows only (open_decoder.cu:181-190)
         if (p->past_lens || p->start_pos != 0) return FLB_ERR_UNSUPPORTED;
         if (p->seq_len > p->total_len) return FLB_ERR_BAD_SHAPE;
+        if ((unsigned long long)p->batch_size * p->head_num * ((p->seq_len + 127) / 128) > 0x7fffffffull) return FLB_ERR_TOO_LARGE;
         if (p->mask_mode == FLB_MASK_GENERIC && p->mask_row_stride < p->seq_len) return FLB_ERR_BAD_SHAPE;
         if (!p->scratch) return FLB_ERR_NULL_POINTER;
         if (!aligned16(p->scratch)) return FLB_ERR_MISALIGNED;
