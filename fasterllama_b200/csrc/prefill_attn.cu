@@ -255,6 +255,12 @@ __device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, Prefill
     return false;
 }
 
+#ifdef FLB_CTATRACE
+// debug build only: four time stamps + SM id per CTA (softmax warp 2, lane 0), after the one-CTA time line's area
+#define CT(k) do { if (warp == 2 && lane == 0) ct[blockIdx.x * 8 + (k)] = globaltimer_ns(); } while (0)
+#else
+#define CT(k) do { } while (0)
+#endif
 #ifdef FLB_TIMELINE
 // debug build only: per-role time stamps of one CTA, written into the (unused with an fp16 cache) K staging area
 #define TL(role, tile, k) do { if (tl_on) tl[((role) * 64 + (tile)) * 4 + (k)] = globaltimer_ns(); } while (0)
@@ -284,6 +290,15 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
     const bool tl_on = (blockIdx.x == gridDim.x / 2 + 1) && (lane == 0);
     uint64_t *tl = reinterpret_cast<uint64_t *>(a.kh);
     if (tl_on && warp == 0) tl[3 * 64 * 4] = globaltimer_ns();
+#endif
+#ifdef FLB_CTATRACE
+    uint64_t *ct = reinterpret_cast<uint64_t *>(a.kh) + 4096;
+    CT(0);
+    if (warp == 2 && lane == 0) {
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        ct[blockIdx.x * 8 + 5] = smid;
+    }
 #endif
     const int nq = (a.S + BM - 1) / BM;
     const int bh = blockIdx.x / nq;
@@ -406,17 +421,18 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
                     ok = issue_s(j + 1);
                     if (!ok) break;
                 }
-                if (!wait_bar(&pb->v_full[s], u & 1u, pb, a.status)) { ok = false; break; }
+                const int vs = j % V_STAGES;
+                if (!wait_bar(&pb->v_full[vs], (uint32_t)(j / V_STAGES) & 1u, pb, a.status)) { ok = false; break; }
                 TL(1, j, 2);
                 if (!wait_bar(&pb->p_full[s], u & 1u, pb, a.status)) { ok = false; break; }
                 TL(1, j, 3);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t db = umma_desc_sw128(aV + s * Cfg::K_TILE_BYTES + kk * 2048, Cfg::K_HALF, 1024);
+                    const uint64_t db = umma_desc_sw128(aV + vs * Cfg::K_TILE_BYTES + kk * 2048, Cfg::K_HALF, 1024);
                     umma_f16_ts(tO, tS[s] + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(&pb->v_empty[s]);
+                umma_commit(&pb->v_empty[vs]);
                 umma_commit(&pb->pv_done);
             }
             if (ok) umma_commit(&pb->o_full);
@@ -442,6 +458,7 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (warp == 2) TL(2, j, 1);
+            if (j == 0) CT(1);
             tc_fence_after();
             // the whole score row of this tile into registers
 #pragma unroll
@@ -537,12 +554,14 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
             if (warp == 2) TL(2, j, 3);
         }
         if (warp == 2) TL(2, 63, 0);
+        CT(2);
 
         // ---- epilogue: O / l
         if (ok) {
             ok = wait_bar(&pb->o_full, 0, pb, a.status);
             ok = __all_sync(0xffffffffu, ok);
         }
+        CT(4);
         if (ok) {
             tc_fence_after();
             const float inv = (l_sum > 0.f) ? 1.0f / l_sum : 0.f; // fully masked row -> zeros
@@ -593,6 +612,7 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
     }
 
     if (warp == 2) TL(2, 63, 1);
+    CT(3);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
