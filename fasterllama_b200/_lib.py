@@ -25,6 +25,8 @@ FLB_ERR_TOO_LARGE = -9
 
 FLB_IN_INT32, FLB_IN_F32, FLB_IN_F16 = 0, 1, 2
 FLB_F32, FLB_F16 = 0, 1
+FLB_MAX_PEERS = 8
+FLB_STATUS_PEER_WAIT = 0x100
 FLB_MASK_NONE, FLB_MASK_GENERIC, FLB_MASK_CAUSAL_INCLUSIVE, FLB_MASK_CAUSAL_STRICT = 0, 1, 2, 3
 
 
@@ -66,6 +68,27 @@ class FlbAttnParams(C.Structure):
         ("split_len", C.c_int),
         ("out_q8", C.c_void_p),
         ("out_q8_scale", C.c_void_p),
+        ("out_peers", C.c_void_p * FLB_MAX_PEERS),
+        ("n_out_peers", C.c_int),
+        ("out_head_total", C.c_int),
+        ("out_head_offset", C.c_int),
+    ]
+
+
+class FlbPeerExchange(C.Structure):
+    """struct flb_peer_exchange, field for field."""
+
+    _fields_ = [
+        ("rank", C.c_int),
+        ("size", C.c_int),
+        ("epoch", C.c_uint),
+        ("flags_local", C.c_void_p),
+        ("flags_peer", C.c_void_p * FLB_MAX_PEERS),
+        ("recv", C.c_void_p),
+        ("dst", C.c_void_p),
+        ("bytes", C.c_size_t),
+        ("status", C.c_void_p),
+        ("timeout_ms", C.c_uint),
     ]
 
 
@@ -83,6 +106,7 @@ EXPORTS = {
     "flb_attn_classify_mask": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_int), C.c_void_p]),
     "flb_attn_scratch_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint), C.c_void_p]),
     "flb_attn_decode_static_scratch": (C.c_int, [_PP, C.c_void_p]),
+    "flb_attn_peer_exchange": (C.c_int, [C.POINTER(FlbPeerExchange), C.c_void_p]),
 }
 
 _lib = None
@@ -111,7 +135,7 @@ def load_library(path: str | None = None) -> C.CDLL:
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.restype = res
         fn.argtypes = args
-    if lib.flb_attn_abi_version() != 2:
+    if lib.flb_attn_abi_version() != 3:
         raise RuntimeError("libflb_attn.so has an unexpected ABI version")
     if path is None:
         _lib = lib

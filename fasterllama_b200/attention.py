@@ -77,6 +77,10 @@ def make_params(
     split_len: int = 0,
     out_q8=None,
     out_q8_scale=None,
+    out_peers=None,
+    out_head_total: int = 0,
+    out_head_offset: int = 0,
+    out_dtype: str | None = None,
 ) -> FlbAttnParams:
     """Fills a `flb_attn_params`.  Shapes: q/k/v [B,S,H,d]; caches [B,H,T,d]; out [B,H,S,d];
     past_lens int32 [B]; freq_cis float32 [rows,d]; attn_mask float32 [*, mask_row_stride]."""
@@ -85,10 +89,10 @@ def make_params(
         raise ValueError("q, k and v must share the shape [B, S, H, d]")
     if tuple(k_cache.shape) != tuple(v_cache.shape) or k_cache.shape[0] != B or k_cache.shape[1] != H or k_cache.shape[3] != d:
         raise ValueError("caches must be [B, H, T, d]")
-    if tuple(out.shape) != (B, H, S, d):
+    if out_peers is None and tuple(out.shape) != (B, H, S, d):
         raise ValueError("out must be [B, H, S, d]")
     for name, t in (("q", q), ("k", k), ("v", v), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
-        if not _is_contiguous(t):
+        if t is not None and not _is_contiguous(t):
             raise ValueError(f"{name} must be contiguous")
     T = int(k_cache.shape[2])
     p = FlbAttnParams()
@@ -109,7 +113,15 @@ def make_params(
     p.k_cache, p.v_cache = _ptr(k_cache), _ptr(v_cache)
     p.cache_dtype = _DT[_dtype_name(k_cache)]
     p.out = _ptr(out)
-    p.out_dtype = _DT[_dtype_name(out)]
+    p.out_dtype = _DT[_dtype_name(out)] if out is not None else _DT[out_dtype or "float32"]  # push form: the peers' element type
+    if out_peers is not None:
+        # head-split push: device addresses (ints) of every rank's [B, out_head_total, 1, d] buffer
+        if len(out_peers) > _lib.FLB_MAX_PEERS:
+            raise ValueError("too many peers")
+        for i, addr in enumerate(out_peers):
+            p.out_peers[i] = int(addr)
+        p.n_out_peers = len(out_peers)
+        p.out_head_total, p.out_head_offset = int(out_head_total), int(out_head_offset)
     p.softmax_scale = float(softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d))
     p.scratch = _ptr(scratch)
     p.scratch_bytes = int(scratch.numel() * scratch.element_size()) if hasattr(scratch, "numel") else (int(scratch.nbytes) if scratch is not None else 0)
@@ -167,6 +179,21 @@ def decode_static_scratch(p: FlbAttnParams, stream=None) -> None:
     """Decode with the library's own fixed scratch block (for callers that cannot provide any):
     `p.scratch` is ignored.  One block per GPU — keep these calls on one stream."""
     _lib.check(_lib.load_library().flb_attn_decode_static_scratch(C.byref(p), _stream_handle(stream)))
+
+
+def peer_exchange(*, rank: int, size: int, epoch: int, flags_local: int, flags_peer, recv: int = 0, dst: int = 0,
+                  nbytes: int = 0, status: int = 0, timeout_ms: int = 0, stream=None) -> None:
+    """The hand-shake that follows a pushing decode call (see `flb_peer_exchange`): all pointers are device
+    addresses; `flags_peer[r]` is rank r's flag array as mapped into this process."""
+    x = _lib.FlbPeerExchange()
+    x.rank, x.size, x.epoch = int(rank), int(size), int(epoch)
+    x.flags_local = int(flags_local)
+    for r, addr in enumerate(flags_peer):
+        x.flags_peer[r] = int(addr) if addr else None
+    x.recv, x.dst, x.bytes = (int(recv) or None), (int(dst) or None), int(nbytes)
+    x.status = int(status) or None
+    x.timeout_ms = int(timeout_ms)
+    _lib.check(_lib.load_library().flb_attn_peer_exchange(C.byref(x), _stream_handle(stream)))
 
 
 def prefill(p: FlbAttnParams, stream=None) -> None:

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libflb_attn.so")
 ORACLE_DIR = os.path.join(ROOT, "oracle")
 ORACLE_LIB = os.path.join(ORACLE_DIR, "libflb_oracle.so")
 
-CUDA_SOURCES = ["decode_attn.cu", "prefill_attn.cu", "launch.cu", "static_scratch.cu"]
+CUDA_SOURCES = ["decode_attn.cu", "prefill_attn.cu", "launch.cu", "static_scratch.cu", "peer_exchange.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",

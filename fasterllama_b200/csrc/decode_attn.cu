@@ -80,6 +80,29 @@ __device__ __forceinline__ float load_input(const DecodeArgs &a, const void *bas
 
 } // namespace
 
+// One element of a finished output row: into `out` [B, H, d], or — head-split layer — into every rank's
+// [B, out_head_total, d] buffer (plain stores; the remote ones travel over NVLink and are published by the
+// exchange kernel that follows on the stream).
+__device__ __forceinline__ void store_out_element(const DecodeArgs &a, int unit, int col, float r) {
+    constexpr int D = kHeadDim;
+    if (a.n_out_peers == 0) {
+        const size_t oo = (size_t)unit * D + col;
+        if (a.out_f16)
+            ((__half *)a.out)[oo] = __float2half_rn(r);
+        else
+            ((float *)a.out)[oo] = r;
+        return;
+    }
+    const int b = unit / a.H, h = unit - b * a.H;
+    const size_t oo = ((size_t)b * a.out_head_total + a.out_head_offset + h) * D + col;
+    if (a.out_f16) {
+        const __half hv = __float2half_rn(r);
+        for (int p = 0; p < a.n_out_peers; ++p) ((__half *)a.out_peers[p])[oo] = hv;
+    } else {
+        for (int p = 0; p < a.n_out_peers; ++p) ((float *)a.out_peers[p])[oo] = r;
+    }
+}
+
 // Fused form of the reference's launchAttnQuantizedTransposeKernel (decoder_kernels.cu:1179-1255) for
 // seq_len == 1: called by every CTA that has just written a head's final output.  The one that is last
 // for its sequence (an arrival counter per sequence; nobody waits) reads the whole [H, d] fp32 row back,
@@ -389,11 +412,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
     if (nsplit == 1) {
         if (tid < D) {
             const float r = (lsum > 0.f) ? acc / lsum : 0.f;
-            const size_t oo = (size_t)unit * D + tid;
-            if (a.out_f16)
-                ((__half *)a.out)[oo] = __float2half_rn(r);
-            else
-                ((float *)a.out)[oo] = r;
+            store_out_element(a, unit, tid, r);
         }
         if (a.out_q8) quantize_row_if_last<NWARPS>(a, b, red, flag);
         return;
@@ -427,11 +446,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
             l2 = fmaf(__ldcg(a.part_ml + (pbase + i) * 2 + 1), e, l2);
         }
         const float r = (l2 > 0.f) ? acc2 / l2 : 0.f;
-        const size_t oo = (size_t)unit * D + tid;
-        if (a.out_f16)
-            ((__half *)a.out)[oo] = __float2half_rn(r);
-        else
-            ((float *)a.out)[oo] = r;
+        store_out_element(a, unit, tid, r);
         if (tid == 0) a.counters[unit] = 0u; // ready for the next call
     }
     if (a.out_q8) quantize_row_if_last<NWARPS>(a, b, red, flag);

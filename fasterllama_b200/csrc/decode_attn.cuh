@@ -39,6 +39,10 @@ struct DecodeArgs {
     unsigned *row_counters; // [B] heads finished per sequence (fused quantisation); zero on entry and exit
     int8_t *out_q8;         // optional [B, H*d] int8 codes of the output row
     float *out_q8_scale;    // optional [B]
+    // optional push of every finished row to n_out_peers buffers [B, out_head_total, d] (peer-mapped), at head
+    // out_head_offset + h; 0 = store into `out` [B, H, d] only
+    void *out_peers[8];
+    int n_out_peers, out_head_total, out_head_offset;
     float *part_o;      // [B*H, nsplit_max, d]
     float *part_ml;     // [B*H, nsplit_max, 2]  (running max in the log2 domain, sum)
 };

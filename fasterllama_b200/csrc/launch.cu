@@ -46,7 +46,20 @@ int check_common(const flb_attn_params *p) {
     if (p->cache_dtype != FLB_F32 && p->cache_dtype != FLB_F16) return FLB_ERR_BAD_ENUM;
     if (p->out_dtype != FLB_F32 && p->out_dtype != FLB_F16) return FLB_ERR_BAD_ENUM;
     if (p->split_len < 0 || (p->split_len % 32) != 0) return FLB_ERR_BAD_SHAPE;
-    if (!p->q || !p->k || !p->v || !p->k_cache || !p->v_cache || !p->out) return FLB_ERR_NULL_POINTER;
+    if (!p->q || !p->k || !p->v || !p->k_cache || !p->v_cache) return FLB_ERR_NULL_POINTER;
+    if (p->n_out_peers < 0 || p->n_out_peers > FLB_MAX_PEERS) return FLB_ERR_BAD_SHAPE;
+    if (p->n_out_peers == 0) {
+        if (!p->out) return FLB_ERR_NULL_POINTER;
+        if (!aligned16(p->out)) return FLB_ERR_MISALIGNED;
+    } else {
+        // head-split push: decode only, every destination given, the local heads inside the full row
+        if (p->seq_len != 1 || p->out_q8) return FLB_ERR_UNSUPPORTED;
+        if (p->out_head_offset < 0 || p->out_head_total < p->out_head_offset + p->head_num) return FLB_ERR_BAD_SHAPE;
+        for (int i = 0; i < p->n_out_peers; ++i) {
+            if (!p->out_peers[i]) return FLB_ERR_NULL_POINTER;
+            if (!aligned16(p->out_peers[i])) return FLB_ERR_MISALIGNED;
+        }
+    }
     if (p->input_mode == FLB_IN_INT32 && (!p->act_scale || !p->q_w_scale || !p->k_w_scale || !p->v_w_scale))
         return FLB_ERR_NULL_POINTER;
     if (p->mask_mode == FLB_MASK_GENERIC) {
@@ -54,7 +67,7 @@ int check_common(const flb_attn_params *p) {
         if (p->mask_row_stride <= 0) return FLB_ERR_BAD_SHAPE;
     }
     if (p->rope_pos0 < 0) return FLB_ERR_BAD_SHAPE;
-    if (!aligned16(p->k_cache) || !aligned16(p->v_cache) || !aligned16(p->out) || !aligned16(p->q) || !aligned16(p->k) ||
+    if (!aligned16(p->k_cache) || !aligned16(p->v_cache) || !aligned16(p->q) || !aligned16(p->k) ||
         !aligned16(p->v))
         return FLB_ERR_MISALIGNED;
     if ((size_t)p->batch_size * p->head_num > (size_t)1 << 24) return FLB_ERR_TOO_LARGE;
@@ -184,6 +197,10 @@ int flb_attn_decode(const flb_attn_params *p, void *cuda_stream) {
     a.row_counters = a.counters + (size_t)p->batch_size * p->head_num;
     a.out_q8 = p->out_q8;
     a.out_q8_scale = p->out_q8_scale;
+    for (int i = 0; i < FLB_MAX_PEERS; ++i) a.out_peers[i] = (i < p->n_out_peers) ? p->out_peers[i] : nullptr;
+    a.n_out_peers = p->n_out_peers;
+    a.out_head_total = p->out_head_total;
+    a.out_head_offset = p->out_head_offset;
     a.part_ml = reinterpret_cast<float *>(sc + l.ml_off);
     a.part_o = reinterpret_cast<float *>(sc + l.o_off);
 

@@ -1,0 +1,118 @@
+// peer_exchange.cu — the exchange step of a head-split (tensor-parallel) decode layer.
+//
+// The decode kernel of every rank stores its finished rows straight into every rank's receive slot
+// (plain peer stores, flb_attn_params::out_peers).  What remains of the all-gather is a hand-shake:
+// tell the others "my rows for this step are in your memory" and learn the same from them.  One small
+// kernel per rank does that, stream-ordered behind the rank's decode kernel:
+//
+//   signal  thread r of block 0 stores `epoch` into word [rank] of rank r's flag array, as a
+//           system-scope release after a system-scope fence: everything this GPU wrote before in
+//           stream order (the pushed rows) is visible to whoever acquires the flag;
+//   wait    threads 0..size-1 of EVERY block poll this rank's own flag words (system-scope acquire)
+//           until word r has reached `epoch`, for at most timeout_ms of wall clock; a wait that runs
+//           out ORs FLB_STATUS_PEER_WAIT into *status and the block skips its copy — nothing spins for
+//           ever, the context stays usable;
+//   copy    the receive slot goes to its final place (16-byte vectors, grid-strided).
+//
+// Blocks do not depend on each other, only on flags written by OTHER GPUs, and each rank signals
+// before it waits, so the ranks cannot dead-lock each other however their kernels are scheduled.
+// Flag words only grow; comparison is by signed difference, so the 32-bit epoch may wrap.
+#include "../../include/flb_attn.h"
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+struct ExchangeArgs {
+    int rank, size;
+    unsigned epoch;
+    unsigned *flags_local;
+    unsigned *flags_peer[FLB_MAX_PEERS];
+    const uint4 *recv;
+    uint4 *dst;
+    size_t n_vec;
+    unsigned *status;
+    unsigned long long timeout_ns;
+};
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(256) flb_peer_exchange_kernel(const ExchangeArgs x) {
+    __shared__ int failed;
+    const int tid = threadIdx.x;
+    if (tid == 0) failed = 0;
+    __syncthreads();
+
+    if (blockIdx.x == 0 && tid < x.size && tid != x.rank) {
+        __threadfence_system();
+        st_release_sys(x.flags_peer[tid] + x.rank, x.epoch);
+    }
+    if (tid < x.size && tid != x.rank) {
+        const unsigned *w = x.flags_local + tid;
+        bool ok = (int)(ld_acquire_sys(w) - x.epoch) >= 0;
+        if (!ok) {
+            const unsigned long long t0 = globaltimer_ns();
+            for (unsigned i = 1; !ok; ++i) {
+                ok = (int)(ld_acquire_sys(w) - x.epoch) >= 0;
+                if (!ok && (i & 15u) == 0) {
+                    if (globaltimer_ns() - t0 > x.timeout_ns) break;
+                    __nanosleep(64);
+                }
+            }
+        }
+        if (!ok) {
+            failed = 1;
+            if (x.status) atomicOr(x.status, FLB_STATUS_PEER_WAIT);
+        }
+    }
+    __syncthreads();
+    if (failed || !x.dst) return;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + tid; i < x.n_vec; i += (size_t)gridDim.x * blockDim.x) x.dst[i] = x.recv[i];
+}
+
+} // namespace
+
+extern "C" int flb_attn_peer_exchange(const flb_peer_exchange *x, void *cuda_stream) {
+    if (!x || !x->flags_local) return FLB_ERR_NULL_POINTER;
+    if (x->size < 1 || x->size > FLB_MAX_PEERS || x->rank < 0 || x->rank >= x->size) return FLB_ERR_BAD_SHAPE;
+    if (x->epoch == 0) return FLB_ERR_BAD_SHAPE;
+    const bool copy = x->dst && x->dst != x->recv && x->bytes > 0;
+    if (copy) {
+        if (!x->recv) return FLB_ERR_NULL_POINTER;
+        if ((x->bytes & 15u) || (reinterpret_cast<uintptr_t>(x->recv) & 15u) || (reinterpret_cast<uintptr_t>(x->dst) & 15u))
+            return FLB_ERR_MISALIGNED;
+    }
+    ExchangeArgs a;
+    a.rank = x->rank;
+    a.size = x->size;
+    a.epoch = x->epoch;
+    a.flags_local = x->flags_local;
+    for (int r = 0; r < FLB_MAX_PEERS; ++r) {
+        a.flags_peer[r] = (r < x->size) ? x->flags_peer[r] : nullptr;
+        if (r < x->size && r != x->rank && !a.flags_peer[r]) return FLB_ERR_NULL_POINTER;
+    }
+    a.recv = static_cast<const uint4 *>(x->recv);
+    a.dst = copy ? static_cast<uint4 *>(x->dst) : nullptr;
+    a.n_vec = copy ? x->bytes / 16 : 0;
+    a.status = x->status;
+    a.timeout_ns = (unsigned long long)(x->timeout_ms ? x->timeout_ms : 1000u) * 1000000ull;
+    // enough blocks to move a decode step's rows (a few hundred KB) in one wave, never more than one per SM
+    size_t blocks = copy ? (a.n_vec + 256 * 4 - 1) / (256 * 4) : 1;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148) blocks = 148;
+    flb_peer_exchange_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(a);
+    return cudaGetLastError() == cudaSuccess ? FLB_OK : FLB_ERR_LAUNCH;
+}

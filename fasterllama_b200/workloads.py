@@ -60,10 +60,14 @@ class Case:
     scratch_zeroed: bool = False
     meta: dict[str, Any] = field(default_factory=dict)
 
-    def params(self, arrays: dict[str, Any] | None = None):
+    def params(self, arrays: dict[str, Any] | None = None, out_peers=None, out_head_total: int = 0, out_head_offset: int = 0):
+        """The parameter block of this case on `arrays`.  With `out_peers` (device addresses of every rank's
+        [B, out_head_total, 1, d] buffer) the decode call pushes its rows there instead of writing `out`."""
         a = arrays if arrays is not None else self.arrays
         return A.make_params(
-            q=a["q"], k=a["k"], v=a["v"], k_cache=a["k_cache"], v_cache=a["v_cache"], out=a["out"],
+            q=a["q"], k=a["k"], v=a["v"], k_cache=a["k_cache"], v_cache=a["v_cache"],
+            out=(None if out_peers is not None else a["out"]), out_peers=out_peers, out_head_total=out_head_total,
+            out_head_offset=out_head_offset, out_dtype=str(a["out"].dtype).replace("torch.", ""),
             scratch=a.get("scratch"), start_pos=self.start_pos, past_lens=a.get("past_lens"),
             max_past_len=self.max_past_len, act_scale=a.get("act_scale"), q_w_scale=a.get("q_w_scale"),
             k_w_scale=a.get("k_w_scale"), v_w_scale=a.get("v_w_scale"), freq_cis=a.get("freq_cis"),

@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define FLB_ATTN_ABI_VERSION 2
+#define FLB_ATTN_ABI_VERSION 3
 
 /* ---- status codes (0 = ok, negative = error) ------------------------------------ */
 typedef enum flb_status {
@@ -72,6 +72,8 @@ typedef enum flb_mask_mode {
 } flb_mask_mode;
 
 /* ---- the parameter block -------------------------------------------------------- */
+#define FLB_MAX_PEERS 8
+
 typedef struct flb_attn_params {
     /* dimensions (names follow OpenDecoder's constructor, open_decoder.h:65) */
     int batch_size;    /* B                                                              */
@@ -147,7 +149,44 @@ typedef struct flb_attn_params {
      * kernel. */
     int8_t *out_q8;
     float *out_q8_scale;
+
+    /* Optional push of the result to several GPUs (decode only; n_out_peers == 0 = off, `out` is used
+     * as above).  For a layer whose heads are split over G GPUs: every rank computes head_num local
+     * heads and each finished output row is stored, by the kernel that produced it, straight into
+     * out_peers[0..n_out_peers-1] — buffers of [B, out_head_total, 1, d] elements of out_dtype, one per
+     * rank (the rank's own included), peer-mapped into this process — at head out_head_offset + h.
+     * `out` is ignored then.  The stores are plain peer stores over NVLink; flb_attn_peer_exchange()
+     * on the same stream publishes them and waits for the other ranks' rows.  Cannot be combined
+     * with out_q8.  No counterpart in the reference (it is single-GPU). */
+    void *out_peers[FLB_MAX_PEERS];
+    int n_out_peers;
+    int out_head_total;
+    int out_head_offset;
 } flb_attn_params;
+
+/* One exchange step between the ranks of a head-split layer (see out_peers above).  Every rank
+ * calls it on its stream after its flb_attn_decode(): the kernel (1) writes `epoch` into word
+ * [rank] of every other rank's flag array (system-scope release: the rows this rank pushed before,
+ * in stream order, are visible first), (2) waits, for at most timeout_ms, until every other rank's
+ * word in flags_local has reached `epoch`, (3) copies `bytes` from recv to dst (skipped when dst is
+ * NULL or equals recv).  A wait that runs out sets FLB_STATUS_PEER_WAIT in *status (a device word,
+ * e.g. the head of the scratch) and skips the copy; the context stays usable.
+ * Rules for the caller: epoch starts at 1 and grows by one per exchange on every rank (flag words
+ * start at 0); the receive buffer has two slots used alternately (slot = epoch & 1), which is
+ * enough because no rank can run two exchanges ahead of another. */
+typedef struct flb_peer_exchange {
+    int rank, size;                       /* size <= FLB_MAX_PEERS                              */
+    unsigned epoch;
+    unsigned *flags_local;                /* [size] this rank's flag words                      */
+    unsigned *flags_peer[FLB_MAX_PEERS];  /* [r] rank r's flag words, peer-mapped ([rank]: unused) */
+    const void *recv;                     /* this rank's receive slot for this epoch            */
+    void *dst;                            /* e.g. qkv_buf_                                      */
+    size_t bytes;                         /* multiple of 16                                     */
+    unsigned *status;                     /* device word, error bits are OR-ed in               */
+    unsigned timeout_ms;                  /* 0 = default (1000)                                 */
+} flb_peer_exchange;
+
+#define FLB_STATUS_PEER_WAIT 0x100u
 
 /* ---- entry points --------------------------------------------------------------- */
 
@@ -211,6 +250,10 @@ int flb_attn_scratch_status(const void *scratch, unsigned *status_out, void *cud
  *     other; keep them on one stream.  The status word read by flb_attn_scratch_status() lives in
  *     the block and is not reachable through this entry point. */
 int flb_attn_decode_static_scratch(const flb_attn_params *p, void *cuda_stream);
+
+/* Signal + bounded wait + copy described at flb_peer_exchange.  One small kernel; no host
+ * synchronisation.  No counterpart in the reference. */
+int flb_attn_peer_exchange(const flb_peer_exchange *x, void *cuda_stream);
 
 #ifdef __cplusplus
 }

@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.EXPORTS), (declared ^ set(_lib.EXPORTS))
     for name in declared:
         assert hasattr(lib, name)
-    assert lib.flb_attn_abi_version() == 2
+    assert lib.flb_attn_abi_version() == 3
 
 
 def test_missing_library_fails_loudly(tmp_path):
@@ -36,12 +36,16 @@ def test_struct_layout_matches_the_header(tmp_path):
     probe = str(tmp_path / "abi_probe.c")
     exe = str(tmp_path / "abi_probe")
     with open(probe, "w") as f:
-        f.write('#include <stdio.h>\n#include "flb_attn.h"\nint main(void){printf("%zu %zu %zu %zu\\n", sizeof(flb_attn_params),'
-                ' offsetof(flb_attn_params, past_lens), offsetof(flb_attn_params, softmax_scale), offsetof(flb_attn_params, out_q8_scale));return 0;}\n')
+        f.write('#include <stdio.h>\n#include "flb_attn.h"\nint main(void){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(flb_attn_params),'
+                ' offsetof(flb_attn_params, past_lens), offsetof(flb_attn_params, softmax_scale), offsetof(flb_attn_params, out_q8_scale),'
+                ' offsetof(flb_attn_params, out_peers), offsetof(flb_attn_params, out_head_offset), sizeof(flb_peer_exchange),'
+                ' offsetof(flb_peer_exchange, flags_peer), offsetof(flb_peer_exchange, timeout_ms));return 0;}\n')
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), probe, "-o", exe], check=True)
     got = [int(x) for x in subprocess.run([exe], check=True, capture_output=True, text=True).stdout.split()]
     P = _lib.FlbAttnParams
-    assert got == [C.sizeof(P), P.past_lens.offset, P.softmax_scale.offset, P.out_q8_scale.offset]
+    X = _lib.FlbPeerExchange
+    assert got == [C.sizeof(P), P.past_lens.offset, P.softmax_scale.offset, P.out_q8_scale.offset, P.out_peers.offset,
+                   P.out_head_offset.offset, C.sizeof(X), X.flags_peer.offset, X.timeout_ms.offset]
 
 
 def _valid_case():
@@ -78,6 +82,16 @@ def test_validate_accepts_a_good_block_and_names_each_fault():
     assert A.validate(p) == _lib.FLB_ERR_BAD_SHAPE
     p = c.params(); p.input_mode = A.FLB_IN_INT32  # scales missing
     assert A.validate(p) == _lib.FLB_ERR_NULL_POINTER
+    # head-split push: destinations, head window and mode are checked; `out` is not needed then
+    p = c.params(); p.n_out_peers = 2; p.out_head_total = 8; p.out_head_offset = 4
+    p.out_peers[0] = p.out; p.out_peers[1] = p.out; p.out = None
+    assert A.validate(p) == _lib.FLB_OK
+    p.out_head_offset = 6  # 6 + 4 local heads > 8
+    assert A.validate(p) == _lib.FLB_ERR_BAD_SHAPE
+    p.out_head_offset = 4; p.out_peers[1] = None
+    assert A.validate(p) == _lib.FLB_ERR_NULL_POINTER
+    p = c.params(); p.n_out_peers = 9
+    assert A.validate(p) == _lib.FLB_ERR_BAD_SHAPE
     assert _lib.load_library().flb_attn_validate(None) == _lib.FLB_ERR_NULL_POINTER
 
 

@@ -72,6 +72,83 @@ def test_head_sharded_layer_on_two_gpus(cuda_device):
     assert ret.get(timeout=10)
 
 
+def _push_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+
+    import datetime
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"),
+                            timeout=datetime.timedelta(seconds=60))
+    window = None
+    try:
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from fasterllama_b200 import attention as A
+        from fasterllama_b200 import workloads as W
+        from fasterllama_b200.tensor_parallel import HeadShardedAttention, PeerWindow
+
+        dev = f"cuda:{rank}"
+        B, H, T = 4, 16, 1300
+        layer = HeadShardedAttention(B, H, world, rank, attend=None)
+        window = PeerWindow(B * H * 128 * 4, world, rank)
+        ok = True
+        # five steps: the two receive slots are reused, the ranks drift apart and meet again
+        for step in range(5):
+            lens = np.array([1200 + step, 37 + step, 512, 700 - step], dtype=np.int32)
+            case = W.host_case("tp-push", 13 + step, B, H, T, past=lens, in_dtype="float16", cache_dtype="float16", out_dtype="float32")
+            full_dev = W.to_device(case, dev)
+            A.forward(case.params(full_dev))
+            want = full_dev["out"].clone()
+
+            fresh = W.to_device(case, dev)
+            fresh.pop("scratch")
+            loc = layer.local_arrays(fresh)
+            loc["scratch"] = torch.zeros(A.workspace_bytes(B, H // world, T), dtype=torch.uint8, device=dev)
+            part = W.Case(name="p", B=B, H=H // world, S=1, T=T, start_pos=0, arrays=loc, rope_add_past=True,
+                          mask_mode=case.mask_mode, max_past_len=case.max_past_len)
+            got = torch.full((B, H, 1, 128), float("nan"), device=dev)
+            if rank == step % world:
+                torch.cuda._sleep(2_000_000)  # about a millisecond of head start for the other rank
+            layer.forward_push(loc, window, lambda l, peers, total, off: part.params(l, out_peers=peers, out_head_total=total, out_head_offset=off),
+                               got, status=loc["scratch"])
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(got, want) and A.scratch_status(loc["scratch"]) == 0
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            ret.put(bool(flag.item()))
+    finally:
+        if window is not None:
+            window.close()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_head_sharded_decode_with_peer_stores_on_two_gpus(cuda_device):
+    """The same layer without a collective library: rows go to the other GPU as peer stores from the decode
+    kernel, a flag hand-shake (bounded wait) replaces the all-gather; bit-identical to the unsharded call."""
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_push_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    codes = [p.exitcode for p in procs]
+    for p in procs:
+        if p.is_alive():
+            p.kill()  # exactly the children started above
+    assert codes == [0, 0]
+    assert ret.get(timeout=10)
+
+
 E2E_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref")
 
 
