@@ -17,6 +17,7 @@
  *   FLB_CACHE_F16=1   keep the caches in fp16 inside the caller's float slabs (first half of each slab)
  *   FLB_MASK_MODE=n   force a flb_mask_mode (default: the caller's additive mask is classified once
  *                     with flb_attn_classify_mask and the matching index-computed mode is used)
+ *   FLB_TP_PUSH=0     tensor-parallel form only: decode steps use ncclAllGather instead of peer stores
  *   FLB_FUSE_QUANT=1  also do the step that follows attention (launchAttnQuantizedTransposeKernel,
  *                     open_decoder.cu:245-246) inside the call; the caller then skips its own launch:
  *                         if (!flb_open_decoder_fused_quant()) launchAttnQuantizedTransposeKernel(...);
@@ -47,14 +48,14 @@ static inline int flb_open_decoder_fused_quant(void) {
 /* attn_q8 / attn_q8_scale: from_tensor_int8_buf_ / from_tensor_scale_buf_ (used when FLB_FUSE_QUANT=1; the scale
  * buffer may be the same memory as from_tensor_scale_buf_ passed as the activation scale: every read of a row's
  * activation scale happens before that row's new scale is written). */
-static inline void flb_open_decoder_attention_core(int batch_size_, int head_num_, int size_per_head_, int total_len_,
-                                                   int seq_len, int start_pos, const int32_t *query_buf_,
-                                                   const int32_t *key_buf_, const int32_t *value_buf_,
-                                                   const float *from_tensor_scale_buf_, const float *q_weight_scale,
-                                                   const float *k_weight_scale, const float *v_weight_scale,
-                                                   const float *freq_cis, const float *attn_mask, float *key_cache_,
-                                                   float *value_cache_, void *scratch, size_t scratch_bytes, float *out,
-                                                   int8_t *attn_q8, float *attn_q8_scale, cudaStream_t stream) {
+static inline void flb_open_decoder_fill_params(flb_attn_params *ap, int batch_size_, int head_num_, int size_per_head_,
+                                                int total_len_, int seq_len, int start_pos, const int32_t *query_buf_,
+                                                const int32_t *key_buf_, const int32_t *value_buf_,
+                                                const float *from_tensor_scale_buf_, const float *q_weight_scale,
+                                                const float *k_weight_scale, const float *v_weight_scale, const float *freq_cis,
+                                                const float *attn_mask, float *key_cache_, float *value_cache_, void *scratch,
+                                                size_t scratch_bytes, float *out, int8_t *attn_q8, float *attn_q8_scale,
+                                                cudaStream_t stream) {
     static int cache_f16 = -1, mask_mode = -1;
     if (cache_f16 < 0) cache_f16 = flb_open_decoder_env_int("FLB_CACHE_F16", 0);
     if (mask_mode < 0) {
@@ -70,47 +71,63 @@ static inline void flb_open_decoder_attention_core(int batch_size_, int head_num
             }
         }
     }
-    flb_attn_params ap;
-    memset(&ap, 0, sizeof(ap));
-    ap.batch_size = batch_size_;
-    ap.head_num = head_num_;
-    ap.size_per_head = size_per_head_;
-    ap.seq_len = seq_len;
-    ap.start_pos = start_pos;
-    ap.total_len = total_len_;
-    ap.input_mode = FLB_IN_INT32;
-    ap.q = query_buf_;
-    ap.k = key_buf_;
-    ap.v = value_buf_;
-    ap.act_scale = from_tensor_scale_buf_;
-    ap.q_w_scale = q_weight_scale;
-    ap.k_w_scale = k_weight_scale;
-    ap.v_w_scale = v_weight_scale;
-    ap.freq_cis = freq_cis; /* row s of this pointer for token s: the reference's rule (decoder_kernels.cu:440) */
-    ap.rope_pos0 = 0;
-    ap.rope_add_past = 0;
-    ap.mask_mode = mask_mode;
-    ap.attn_mask = attn_mask;
-    ap.mask_row_stride = total_len_;
-    ap.k_cache = key_cache_;
-    ap.v_cache = value_cache_;
-    ap.cache_dtype = cache_f16 ? FLB_F16 : FLB_F32;
-    ap.out = out;
-    ap.out_dtype = FLB_F32;
-    ap.softmax_scale = 1.0f / sqrtf((float)size_per_head_);
-    ap.scratch = scratch;
-    ap.scratch_bytes = scratch_bytes;
-    ap.scratch_zeroed = 0;
+    memset(ap, 0, sizeof(*ap));
+    ap->batch_size = batch_size_;
+    ap->head_num = head_num_;
+    ap->size_per_head = size_per_head_;
+    ap->seq_len = seq_len;
+    ap->start_pos = start_pos;
+    ap->total_len = total_len_;
+    ap->input_mode = FLB_IN_INT32;
+    ap->q = query_buf_;
+    ap->k = key_buf_;
+    ap->v = value_buf_;
+    ap->act_scale = from_tensor_scale_buf_;
+    ap->q_w_scale = q_weight_scale;
+    ap->k_w_scale = k_weight_scale;
+    ap->v_w_scale = v_weight_scale;
+    ap->freq_cis = freq_cis; /* row s of this pointer for token s: the reference's rule (decoder_kernels.cu:440) */
+    ap->rope_pos0 = 0;
+    ap->rope_add_past = 0;
+    ap->mask_mode = mask_mode;
+    ap->attn_mask = attn_mask;
+    ap->mask_row_stride = total_len_;
+    ap->k_cache = key_cache_;
+    ap->v_cache = value_cache_;
+    ap->cache_dtype = cache_f16 ? FLB_F16 : FLB_F32;
+    ap->out = out;
+    ap->out_dtype = FLB_F32;
+    ap->softmax_scale = 1.0f / sqrtf((float)size_per_head_);
+    ap->scratch = scratch;
+    ap->scratch_bytes = scratch_bytes;
+    ap->scratch_zeroed = 0;
     if (flb_open_decoder_fused_quant()) {
-        ap.out_q8 = attn_q8;
-        ap.out_q8_scale = attn_q8_scale;
+        ap->out_q8 = attn_q8;
+        ap->out_q8_scale = attn_q8_scale;
     }
-    const int st = flb_attn_forward(&ap, stream);
+}
+
+/* Errors follow the reference's convention: print, then exit(1). */
+static inline void flb_open_decoder_check(int st, const char *what, int line) {
     if (st != FLB_OK) {
-        printf("CUDA Error:\n    File:   %s\n    Line:   %d\n    flb_attn status: %d (%s)\n", __FILE__, __LINE__, st,
-               flb_status_string(st));
+        printf("CUDA Error:\n    File:   %s\n    Line:   %d\n    %s status: %d (%s)\n", __FILE__, line, what, st, flb_status_string(st));
         exit(1);
     }
+}
+
+static inline void flb_open_decoder_attention_core(int batch_size_, int head_num_, int size_per_head_, int total_len_,
+                                                   int seq_len, int start_pos, const int32_t *query_buf_,
+                                                   const int32_t *key_buf_, const int32_t *value_buf_,
+                                                   const float *from_tensor_scale_buf_, const float *q_weight_scale,
+                                                   const float *k_weight_scale, const float *v_weight_scale,
+                                                   const float *freq_cis, const float *attn_mask, float *key_cache_,
+                                                   float *value_cache_, void *scratch, size_t scratch_bytes, float *out,
+                                                   int8_t *attn_q8, float *attn_q8_scale, cudaStream_t stream) {
+    flb_attn_params ap;
+    flb_open_decoder_fill_params(&ap, batch_size_, head_num_, size_per_head_, total_len_, seq_len, start_pos, query_buf_, key_buf_,
+                                 value_buf_, from_tensor_scale_buf_, q_weight_scale, k_weight_scale, v_weight_scale, freq_cis,
+                                 attn_mask, key_cache_, value_cache_, scratch, scratch_bytes, out, attn_q8, attn_q8_scale, stream);
+    flb_open_decoder_check(flb_attn_forward(&ap, stream), "flb_attn", __LINE__);
 }
 
 /* The call OpenDecoder::forward makes: scratch = query_out_buf_ .. end of qk_buf_ (3 * buf_size floats + the score
@@ -137,6 +154,9 @@ static inline void flb_open_decoder_attention(int batch_size_, int head_num_, in
  * calls flb_open_decoder_attention_tp() on those heads against its own cache shard (the first 1/size of
  * every layer's slab), and gets the full [B,H,S,d] attention output back through ONE exchange: an
  * all-gather of the fp32 head outputs (the next kernel needs the absmax over all heads of a token row).
+ * Prefill does it with ncclAllGather; decode steps (small, latency-bound, 32 per token) do it without a
+ * collective call: the decode kernel stores its rows into every rank's receive slot as peer stores and
+ * flb_attn_peer_exchange() does the flag hand-shake (FLB_TP_PUSH=0 keeps NCCL there too).
  * Everything after that stays replicated.  Exactly one translation unit defines
  * FLB_OPEN_DECODER_TP_STATE before including this header; it holds the communicator. */
 #ifdef FLB_WITH_NCCL
@@ -145,15 +165,76 @@ static inline void flb_open_decoder_attention(int batch_size_, int head_num_, in
 typedef struct flb_tp_state_t {
     ncclComm_t comm;
     int rank, size;
+    /* decode steps without NCCL (see flb_tp_push_setup): 0 = not set up yet, 1 = in use, -1 = not available */
+    int push_ready;
+    unsigned push_epoch;
+    size_t push_slot_bytes;
+    unsigned char *push_base[FLB_MAX_PEERS]; /* [r]: rank r's block (256 B of flag words + two receive slots) as mapped here */
 } flb_tp_state_t;
 #ifdef FLB_OPEN_DECODER_TP_STATE
-flb_tp_state_t flb_tp_state = {0, 0, 1};
+flb_tp_state_t flb_tp_state = {0, 0, 1, 0, 0, 0, {0}};
 #else
 extern flb_tp_state_t flb_tp_state;
 #endif
 
 static inline int flb_tp_size(void) { return flb_tp_state.size; }
 static inline int flb_tp_rank(void) { return flb_tp_state.rank; }
+
+/* One-time set-up of the decode exchange that needs no collective call per layer: every rank allocates one block
+ * (flag words + two receive slots of slot_bytes), the CUDA IPC handles travel through the communicator once, and
+ * every rank maps the others' blocks (which also enables peer access).  All ranks take the same decision: an
+ * all-reduce(min) of "it worked here" ends the set-up, so either every rank pushes or every rank keeps NCCL.
+ * The block lives until the process ends.  FLB_TP_PUSH=0 keeps the NCCL all-gather for decode as well. */
+static inline void flb_tp_push_setup(size_t slot_bytes, cudaStream_t stream) {
+    flb_tp_state_t *s = &flb_tp_state;
+    const int g = s->size;
+    int ok = (g <= FLB_MAX_PEERS) && flb_open_decoder_env_int("FLB_TP_PUSH", 1) != 0;
+    unsigned char *own = NULL, *stage = NULL;
+    cudaIpcMemHandle_t mine, all[FLB_MAX_PEERS];
+    slot_bytes = (slot_bytes + 255) / 256 * 256;
+    const size_t total = 256 + 2 * slot_bytes;
+    memset(&mine, 0, sizeof(mine));
+    if (ok && (cudaMalloc((void **)&own, total) != cudaSuccess || cudaMemsetAsync(own, 0, total, stream) != cudaSuccess ||
+               cudaIpcGetMemHandle(&mine, own) != cudaSuccess))
+        ok = 0;
+    /* handles (64 bytes each) and the verdict go through the communicator: the ranks stay in step whatever happened */
+    if (cudaMalloc((void **)&stage, (size_t)(g + 1) * 64 + 16) != cudaSuccess) {
+        printf("flb_tp_push_setup: cudaMalloc failed\n");
+        exit(1);
+    }
+    cudaMemcpyAsync(stage + (size_t)g * 64, &mine, 64, cudaMemcpyHostToDevice, stream);
+    ncclAllGather(stage + (size_t)g * 64, stage, 64, ncclChar, s->comm, stream);
+    cudaMemcpyAsync(all, stage, (size_t)g * 64, cudaMemcpyDeviceToHost, stream);
+    cudaStreamSynchronize(stream);
+    for (int r = 0; r < g && ok; ++r) {
+        if (r == s->rank) {
+            s->push_base[r] = own;
+        } else if (cudaIpcOpenMemHandle((void **)&s->push_base[r], all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            ok = 0;
+        }
+    }
+    int *verdict = (int *)(stage + (size_t)(g + 1) * 64);
+    cudaMemcpyAsync(verdict, &ok, sizeof(int), cudaMemcpyHostToDevice, stream);
+    ncclAllReduce(verdict, verdict, 1, ncclInt, ncclMin, s->comm, stream);
+    cudaMemcpyAsync(&ok, verdict, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    cudaStreamSynchronize(stream);
+    cudaGetLastError(); /* a failed IPC call above is handled by the verdict, not left as a sticky error text */
+    cudaFree(stage);
+    s->push_slot_bytes = slot_bytes;
+    s->push_epoch = 0;
+    s->push_ready = ok ? 1 : -1;
+}
+
+/* Error bits the exchange kernels have left since set-up (FLB_STATUS_PEER_WAIT: a rank did not show up in time and
+ * that step's rows were not delivered).  Synchronises the stream; 0 also when the push path is not in use. */
+static inline unsigned flb_tp_push_status(cudaStream_t stream) {
+    unsigned v = 0;
+    if (flb_tp_state.push_ready == 1) {
+        cudaMemcpyAsync(&v, flb_tp_state.push_base[flb_tp_state.rank] + 128, sizeof(v), cudaMemcpyDeviceToHost, stream);
+        cudaStreamSynchronize(stream);
+    }
+    return v;
+}
 
 static inline void flb_open_decoder_attention_tp(int batch_size_, int head_num_, int size_per_head_, int max_prompt_len_,
                                                  int total_len_, int seq_len, int start_pos, const int32_t *query_buf_,
@@ -178,6 +259,43 @@ static inline void flb_open_decoder_attention_tp(int batch_size_, int head_num_,
      * output [B,h_local,S,d] (at most half of it with two ranks or more). */
     const size_t buf_size = (size_t)(qk_buf_ - query_out_buf_) / 3;
     float *local_out = query_out_buf_ + 2 * buf_size;
+    if (seq_len == 1) {
+        /* decode: the kernel stores each finished head row into every rank's receive slot (peer stores over NVLink);
+         * one small kernel then signals, waits (bounded) and moves the slot into qkv_buf_.  No collective call. */
+        const size_t row_bytes = sizeof(float) * (size_t)batch_size_ * head_num_ * size_per_head_;
+        if (flb_tp_state.push_ready == 0) flb_tp_push_setup(row_bytes, stream);
+        if (flb_tp_state.push_ready == 1 && row_bytes <= flb_tp_state.push_slot_bytes) {
+            flb_tp_state_t *s = &flb_tp_state;
+            const unsigned epoch = ++s->push_epoch;
+            const size_t slot_off = 256 + (size_t)(epoch & 1u) * s->push_slot_bytes;
+            flb_attn_params ap;
+            flb_open_decoder_fill_params(&ap, batch_size_, h_local, size_per_head_, total_len_, seq_len, start_pos, query_buf_, key_buf_,
+                                         value_buf_, from_tensor_scale_buf_, q_weight_scale + col0, k_weight_scale + col0,
+                                         v_weight_scale + col0, freq_cis, attn_mask, key_cache_, value_cache_, query_out_buf_,
+                                         sizeof(float) * 2 * buf_size, NULL, NULL, NULL, stream);
+            ap.out_q8 = NULL;
+            ap.out_q8_scale = NULL;
+            ap.n_out_peers = g;
+            ap.out_head_total = head_num_;
+            ap.out_head_offset = r * h_local;
+            for (int i = 0; i < g; ++i) ap.out_peers[i] = s->push_base[i] + slot_off;
+            flb_open_decoder_check(flb_attn_decode(&ap, stream), "flb_attn_decode", __LINE__);
+            flb_peer_exchange x;
+            memset(&x, 0, sizeof(x));
+            x.rank = r;
+            x.size = g;
+            x.epoch = epoch;
+            x.flags_local = (unsigned *)s->push_base[r];
+            for (int i = 0; i < g; ++i) x.flags_peer[i] = (unsigned *)s->push_base[i];
+            x.recv = s->push_base[r] + slot_off;
+            x.dst = qkv_buf_;
+            x.bytes = row_bytes;
+            x.status = (unsigned *)(s->push_base[r] + 128); /* sticky: read it with flb_tp_push_status() */
+            x.timeout_ms = 2000;
+            flb_open_decoder_check(flb_attn_peer_exchange(&x, stream), "flb_attn_peer_exchange", __LINE__);
+            return;
+        }
+    }
     flb_open_decoder_attention_core(batch_size_, h_local, size_per_head_, total_len_, seq_len, start_pos, query_buf_, key_buf_,
                                     value_buf_, from_tensor_scale_buf_, q_weight_scale + col0, k_weight_scale + col0,
                                     v_weight_scale + col0, freq_cis, attn_mask, key_cache_, value_cache_, query_out_buf_,

@@ -150,12 +150,15 @@ def main():
     ap.add_argument("--mask", default="inclusive", choices=["inclusive", "strict"])
     ap.add_argument("--cache-f16", action="store_true")
     ap.add_argument("--fuse-quant", action="store_true", help="adaptor also does the attention-output quantisation")
+    ap.add_argument("--no-push", action="store_true", help="tp: decode steps use ncclAllGather instead of peer stores")
     ap.add_argument("--repeat", type=int, default=1, help="runs; the time of the last one is reported")
     args = ap.parse_args()
     if args.cache_f16:
         os.environ["FLB_CACHE_F16"] = "1"
     if args.fuse_quant:
         os.environ["FLB_FUSE_QUANT"] = "1"
+    if args.no_push:
+        os.environ["FLB_TP_PUSH"] = "0"
     cfg = CONFIGS[args.config]
     rank, world, local = tp_init(args.variant)
     for _ in range(args.repeat):
@@ -171,7 +174,9 @@ def main():
         return
     np.savez(args.out, ids=ids, seq_len=sl, ms=ms)
     toks = cfg["batch"] * cfg["max_gen_len"]
-    print(json.dumps({"variant": args.variant, "tp": world, "config": args.config, "mask": args.mask, "cache_f16": bool(args.cache_f16),
+    push = bool(load(args.variant).e2e_tp_push_in_use()) if (args.variant == "tp" and world > 1) else False
+    print(json.dumps({"variant": args.variant, "tp": world, "tp_decode_exchange": ("peer stores" if push else ("nccl" if world > 1 else None)),
+                      "config": args.config, "mask": args.mask, "cache_f16": bool(args.cache_f16),
                       "ms": round(ms, 2), "tokens_per_s": round(toks / ms * 1e3, 1), "first_ids": ids[0, :8].tolist(),
                       "seq_len": sl[:4].tolist()}))
 

@@ -54,6 +54,8 @@ int e2e_tp_unique_id(char *out128) {
     memcpy(out128, &id, sizeof(id));
     return 0;
 }
+// 1 when the decode steps of the last run went through peer stores, 0 when they used ncclAllGather
+int e2e_tp_push_in_use(void) { return flb_tp_state.push_ready == 1 ? 1 : 0; }
 int e2e_tp_init(int rank, int size, int device, const char *id128) {
     cudaSetDevice(device);
     ncclUniqueId id;
@@ -125,6 +127,12 @@ int e2e_run(const e2e_args *a, float *ms) {
     dec->forward(param, dp);
     cudaEventRecord(e1, stream);
     cudaError_t ce = cudaStreamSynchronize(stream);
+#ifdef FLB_WITH_NCCL
+    // the decode steps' exchange kernels report a rank that did not show up through a sticky status word
+    const unsigned push_status = (ce == cudaSuccess) ? flb_tp_push_status(stream) : 0u;
+#else
+    const unsigned push_status = 0u;
+#endif
     float t = 0.f;
     cudaEventElapsedTime(&t, e0, e1);
     if (ms) *ms = t;
@@ -135,6 +143,7 @@ int e2e_run(const e2e_args *a, float *ms) {
     cudaStreamDestroy(stream);
     cublasDestroy(handle);
     if (ce != cudaSuccess) return 2000 + (int)ce;
+    if (push_status) return 3000 + (int)(push_status & 0x3ffu);
     ce = cudaGetLastError();
     return ce == cudaSuccess ? 0 : 2000 + (int)ce;
 }

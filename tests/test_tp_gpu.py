@@ -155,12 +155,15 @@ E2E_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.skipif(not all(os.path.exists(os.path.join(E2E_DIR, f"libe2e_{v}.so")) for v in ("flb", "tp")),
                     reason="end-to-end libraries not built")
+@pytest.mark.parametrize("exchange", ["peer stores", "nccl"])
 @pytest.mark.parametrize("config", ["small", "medium"])
-def test_tensor_parallel_generation_matches_one_gpu(cuda_device, tmp_path, config):
+def test_tensor_parallel_generation_matches_one_gpu(cuda_device, tmp_path, config, exchange):
     """The reference's DecodingSampling with the tensor-parallel layer (Q/K/V projections on a column slice,
-    head-sharded attention, one NCCL all-gather of head outputs per layer) on two GPUs samples exactly the
+    head-sharded attention, one exchange of head outputs per layer: NCCL all-gather in prefill; in decode either
+    peer stores from the decode kernel + flag hand-shake, or NCCL again) on two GPUs samples exactly the
     ids of the one-GPU adaptor run: int32 projections are exact under the column split, each head's
-    attention is bit-identical wherever it runs, and the gather is a copy."""
+    attention is bit-identical wherever it runs, and the exchange is a copy."""
+    import json
     import subprocess
 
     root = os.path.dirname(E2E_DIR.rstrip("/"))
@@ -172,9 +175,12 @@ def test_tensor_parallel_generation_matches_one_gpu(cuda_device, tmp_path, confi
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-                        "--master-port", str(port), e2e, "--variant", "tp", "--config", config, "--out", two],
+                        "--master-port", str(port), e2e, "--variant", "tp", "--config", config, "--out", two]
+                       + (["--no-push"] if exchange == "nccl" else []),
                        capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1]
+    assert json.loads(line)["tp_decode_exchange"] == exchange
     a, b = np.load(one), np.load(two)
     assert np.array_equal(a["seq_len"], b["seq_len"])
     assert np.array_equal(a["ids"], b["ids"])
