@@ -164,3 +164,29 @@ def test_out_of_range_length_is_flagged_not_followed(cuda_device):
     A.forward(case.params(dev))
     torch.cuda.synchronize()
     assert A.scratch_status(dev["scratch"]) == 0
+
+
+@pytest.mark.parametrize("in_dtype,cache_dtype,out_dtype", [("float16", "float16", "float16"), ("int32", "float32", "float32")])
+def test_pinned_host_inputs_and_output(cuda_device, in_dtype, cache_dtype, out_dtype):
+    """q, k, v (and the scales) and the output may live in pinned host memory: the kernel reads and writes them
+    over the bus, the caches and the scratch stay on the device.  Same results, bit for bit, as with device
+    buffers."""
+    import torch
+
+    past = np.array([1200, 3, 513], dtype=np.int32)
+    case = W.host_case("pinned", 77, 3, 8, 1300, past=past, in_dtype=in_dtype, cache_dtype=cache_dtype, out_dtype=out_dtype)
+    want = run_cuda(case)
+    assert want["status"] == 0
+    dev = W.to_device(case, cuda_device)
+    host_names = ("q", "k", "v", "act_scale", "q_w_scale", "k_w_scale", "v_w_scale")
+    arrays = dict(dev)
+    for n in host_names:
+        if n in arrays and arrays[n] is not None:
+            arrays[n] = arrays[n].cpu().pin_memory()
+    arrays["out"] = torch.full_like(dev["out"], float("nan"), device="cpu").pin_memory()
+    A.forward(case.params(arrays))
+    torch.cuda.synchronize()
+    assert A.scratch_status(dev["scratch"]) == 0
+    assert np.array_equal(arrays["out"].float().numpy(), want["out"])
+    assert np.array_equal(dev["k_cache"].float().cpu().numpy(), want["k_cache"])
+    assert np.array_equal(dev["v_cache"].float().cpu().numpy(), want["v_cache"])
