@@ -195,6 +195,7 @@ def run_ours(args, rank, world, local):
     for j in range(NBUF):
         c = W.device_case(f"{args.workload}-{j}", seed + 7919 * j + 104729 * rank, B, H, T, lens, device=dev)
         c.scratch_zeroed = True  # device_case hands over zeroed scratch; the kernel leaves it zeroed
+        c.early_start = not args.no_early_start
         # q, k, v as three views of one buffer, so that the end-to-end leg moves them with one host->device copy
         c.arrays["qkv"] = torch.stack([c.arrays[n] for n in ("q", "k", "v")]).contiguous()
         c.arrays["q"], c.arrays["k"], c.arrays["v"] = c.arrays["qkv"][0], c.arrays["qkv"][1], c.arrays["qkv"][2]
@@ -279,7 +280,10 @@ def run_ours(args, rank, world, local):
         "vs_baseline": None, "dtype": "f16 storage, f32 arithmetic", "data": "synthetic",
         "config": {
             "workload": desc, "per_gpu_batch": B, "heads": H, "head_dim": 128, "cache_rows_total": int(lens.sum()),
-            "total_len": T, "split_len": 512, "l2": f"{NBUF} distinct input sets rotated ({NBUF * bytes_step / 1e6:.0f} MB > 126 MB L2), no flush kernel in the timed region",
+            "total_len": T, "split_len": 512,
+            "launch": ("programmatic dependent launch: a call's CTAs may become resident and fetch their first cache tiles while the previous call drains; inputs, scratch and outputs are touched only after it has completed"
+                       if not args.no_early_start else "ordinary stream launches"),
+            "l2": f"{NBUF} distinct input sets rotated ({NBUF * bytes_step / 1e6:.0f} MB > 126 MB L2), no flush kernel in the timed region",
             "sharding": ("one batch split over the ranks by contiguous (batch, head) ranges, no collective" if strong
                          else "every rank runs its own batch of this shape (independent (batch, head) units), no collective"),
         },
@@ -598,6 +602,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + list(PREFILL_WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the host-oracle baseline leg")
+    ap.add_argument("--no-early-start", action="store_true",
+                    help="launch every decode call the ordinary way (default: programmatic dependent launch, a call may fetch its first cache tiles while the previous one drains)")
     ap.add_argument("--e2e-mode", default="mapped", choices=["mapped", "copies"],
                     help="end-to-end leg: hand the pinned host buffers to the call (the kernel moves the bytes) or copy in / copy out")
     ap.add_argument("--sets", type=int, default=NBUF, help="distinct input sets rotated through the loop (1 for a small profiler capture)")

@@ -72,6 +72,7 @@ class FlbAttnParams(C.Structure):
         ("n_out_peers", C.c_int),
         ("out_head_total", C.c_int),
         ("out_head_offset", C.c_int),
+        ("early_start", C.c_int),
     ]
 
 

@@ -178,11 +178,13 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
     // a length outside [0, T-1] or beyond what the grid was sized for is flagged and clamped so
     // that no access leaves the slab
     const int past_cap = min(a.T - 1, a.nsplit_max * a.split_len);
-    if (past < 0 || past > past_cap) {
-        if (threadIdx.x == 0 && split == 0) atomicOr(a.status, 4u);
-        past = max(0, min(past, past_cap));
-    }
+    const bool bad_len = (past < 0 || past > past_cap); // reported by thread 0 once global writes are allowed
+    past = max(0, min(past, past_cap));
     const int nsplit = max(1, (past + a.split_len - 1) / a.split_len);
+    // Early start (programmatic dependent launch): the call that follows on the stream may begin as soon as
+    // every CTA of this grid has got this far; until its own grid_dependency_wait() it only fetches cache rows
+    // that are older than this call (and reads past_lens), which the caller has promised are settled.
+    if (a.early_start) grid_launch_dependents();
     if (split >= nsplit) return;
 
     const int row0 = split * a.split_len;
@@ -228,6 +230,9 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
     } else {
         // ---------------- compute warps ------------------------------------------------------
         const int tid = threadIdx.x; // < NC
+        // everything below reads this step's inputs or writes global memory: the previous kernel must be done
+        if (a.early_start) grid_dependency_wait();
+        if (bad_len && tid == 0 && split == 0) atomicOr(a.status, 4u);
         // -- the new token: dequantise, rotate, append (a2, a3, a4 of the reference in one place)
         {
             float qraw = 0.f, kraw = 0.f, vraw = 0.f;
@@ -463,8 +468,21 @@ static cudaError_t launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const unsigned grid = (unsigned)a.B * (unsigned)a.H * (unsigned)a.nsplit_max;
-    kern<<<grid, (NWARPS + 1) * 32, smem, stream>>>(a);
-    return cudaGetLastError();
+    if (!a.early_start) {
+        kern<<<grid, (NWARPS + 1) * 32, smem, stream>>>(a);
+        return cudaGetLastError();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3((NWARPS + 1) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
 cudaError_t launch_decode(const DecodeArgs &a, bool cache_f16, cudaStream_t stream) {

@@ -43,6 +43,7 @@ struct DecodeArgs {
     // out_head_offset + h; 0 = store into `out` [B, H, d] only
     void *out_peers[8];
     int n_out_peers, out_head_total, out_head_offset;
+    int early_start; // launched with programmatic stream serialisation: cache tiles may be fetched before the wait
     float *part_o;      // [B*H, nsplit_max, d]
     float *part_ml;     // [B*H, nsplit_max, 2]  (running max in the log2 domain, sum)
 };

@@ -58,6 +58,13 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Programmatic dependent launch.  Both are no-ops in a kernel launched the ordinary way.
+// launch_dependents: the next kernel on the stream, if it was launched with programmatic stream serialisation,
+// may start once every CTA of this grid has executed this (or exited).  wait: blocks until the kernels this grid
+// depends on have completed and their writes are visible.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -201,6 +201,7 @@ int flb_attn_decode(const flb_attn_params *p, void *cuda_stream) {
     a.n_out_peers = p->n_out_peers;
     a.out_head_total = p->out_head_total;
     a.out_head_offset = p->out_head_offset;
+    a.early_start = (p->early_start != 0 && p->scratch_zeroed != 0) ? 1 : 0;
     a.part_ml = reinterpret_cast<float *>(sc + l.ml_off);
     a.part_o = reinterpret_cast<float *>(sc + l.o_off);
 

@@ -58,6 +58,7 @@ class Case:
     split_len: int = 0
     max_past_len: int = 0
     scratch_zeroed: bool = False
+    early_start: bool = False  # decode: programmatic dependent launch (see flb_attn_params.early_start)
     meta: dict[str, Any] = field(default_factory=dict)
 
     def params(self, arrays: dict[str, Any] | None = None, out_peers=None, out_head_total: int = 0, out_head_offset: int = 0):
@@ -73,7 +74,7 @@ class Case:
             k_w_scale=a.get("k_w_scale"), v_w_scale=a.get("v_w_scale"), freq_cis=a.get("freq_cis"),
             rope_pos0=self.rope_pos0, rope_add_past=self.rope_add_past, mask_mode=self.mask_mode,
             attn_mask=a.get("attn_mask"), softmax_scale=self.softmax_scale,
-            scratch_zeroed=self.scratch_zeroed, split_len=self.split_len,
+            scratch_zeroed=self.scratch_zeroed, split_len=self.split_len, early_start=self.early_start,
             out_q8=a.get("out_q8"), out_q8_scale=a.get("out_q8_scale"),
         )
 

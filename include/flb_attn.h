@@ -165,6 +165,16 @@ typedef struct flb_attn_params {
     int n_out_peers;
     int out_head_total;
     int out_head_offset;
+
+    /* Decode only, optional: early_start != 0 launches the kernel with programmatic stream
+     * serialisation.  Its CTAs may then become resident, and fetch their first cache tiles, while the
+     * previous kernel on the stream is still draining; q, k, v, the scales, the scratch and every
+     * output are touched only after that kernel has completed (griddepcontrol.wait).  The caller
+     * promises that the cache rows below each sequence's length and past_lens were final BEFORE the
+     * previous kernel on the stream started (true in the decoder layer: the kernel in front is the
+     * QKV projection).  Needs scratch_zeroed != 0 (a memset in front would serialise anyway); ignored
+     * otherwise.  A decode kernel launched this way also lets the next such call start early. */
+    int early_start;
 } flb_attn_params;
 
 /* One exchange step between the ranks of a head-split layer (see out_peers above).  Every rank

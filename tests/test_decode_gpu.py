@@ -190,3 +190,30 @@ def test_pinned_host_inputs_and_output(cuda_device, in_dtype, cache_dtype, out_d
     assert np.array_equal(arrays["out"].float().numpy(), want["out"])
     assert np.array_equal(dev["k_cache"].float().cpu().numpy(), want["k_cache"])
     assert np.array_equal(dev["v_cache"].float().cpu().numpy(), want["v_cache"])
+
+
+def test_early_start_calls_back_to_back(cuda_device):
+    """Programmatic dependent launch: a chain of decode calls that may each start while the one before drains
+    gives the same bits as ordinary launches — on rotating buffer sets and on one set reused by every call."""
+    import torch
+
+    from fasterllama_b200 import workloads as W2
+
+    lens = W2.draw_lengths(5, 6, 200, 1500)
+    outs = {}
+    for early in (False, True):
+        sets = []
+        for j in range(3):
+            c = W2.device_case("early", 50 + j, 6, 8, 1501, lens, device=cuda_device)
+            c.scratch_zeroed = True
+            c.early_start = early
+            sets.append((c, c.params()))
+        for i in range(12):
+            A.decode(sets[i % 3][1])
+        for _ in range(4):
+            A.decode(sets[0][1])  # the same buffers, scratch and counters in consecutive launches
+        torch.cuda.synchronize()
+        assert all(A.scratch_status(c.arrays["scratch"]) == 0 for c, _ in sets)
+        outs[early] = [c.arrays["out"].clone() for c, _ in sets] + [c.arrays["k_cache"].clone() for c, _ in sets]
+    for a, b in zip(outs[False], outs[True]):
+        assert torch.equal(a, b)
