@@ -451,7 +451,7 @@ def run_reference(args, rank, world, local):
     from fasterllama_b200 import workloads as W
 
     if args.workload in PREFILL_WORKLOADS:
-        return run_reference_prefill(args, local)
+        return run_reference_prefill(args, local, world)
     B, H, lo, hi, seed, desc = WORKLOADS[args.workload]
     T, d = hi + 1, 128
     dev = f"cuda:{local}"
@@ -530,6 +530,7 @@ def run_reference(args, rank, world, local):
     e2e_val = bytes_step * steps / t_e2e / 1e9
     line = {
         "impl": "reference", "metric": "decode_attn_hbm_gbps", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1,
+        "ranks_launched": world,  # the reference is single-GPU: rank 0 alone measures, the others exit
         "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": round(t / steps * 1e3, 5), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": desc, "reference_mode": "the reference's kernels + cuBLAS gemv with corrected arguments (as written cuBLAS rejects them for L > 128), fp32 cache, one call per sequence (it has one cached length per call)",
@@ -546,7 +547,7 @@ def run_reference(args, rank, world, local):
     ref.close()
 
 
-def run_reference_prefill(args, local):
+def run_reference_prefill(args, local, world=1):
     """The reference's prefill chain (3 kernels, 2 batched cuBLAS GEMMs with fp16 tensor-core math on
     fp32 storage, softmax over the materialised 1 GiB score matrix) at the config-3 shape."""
     from fasterllama_b200 import workloads as W
@@ -581,7 +582,7 @@ def run_reference_prefill(args, local):
     tt = e0.elapsed_time(e1) * 1e-3
     flops = B * H * 2 * d * S * (S + 1)
     v = flops * steps / tt / 1e12
-    line = {"impl": "reference", "metric": "prefill_attn_tflops", "value": round(v, 1), "unit": "TFLOP/s", "n_gpus": 1,
+    line = {"impl": "reference", "metric": "prefill_attn_tflops", "value": round(v, 1), "unit": "TFLOP/s", "n_gpus": 1, "ranks_launched": world,
             "steps": steps, "warmup": 3, "ms_per_step": round(tt / steps * 1e3, 5), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32 storage, fp16 tensor-core math (CUBLAS_COMPUTE_32F_FAST_16F)", "data": "synthetic",
             "config": {"workload": "causal prefill attention, batch 8, 1024 tokens, 32 heads x 128", "flop_basis": "causal-exact flops, identical to the other arm (the reference computes the full square)"},
