@@ -17,6 +17,8 @@
  *   FLB_CACHE_F16=1   keep the caches in fp16 inside the caller's float slabs (first half of each slab)
  *   FLB_MASK_MODE=n   force a flb_mask_mode (default: the caller's additive mask is classified once
  *                     with flb_attn_classify_mask and the matching index-computed mode is used)
+ *   FLB_EARLY_START=0 decode calls keep a counter memset and an ordinary launch each (default: only the first
+ *                     decode call after a prefill clears the counters, the others start early, see below)
  *   FLB_TP_PUSH=0     tensor-parallel form only: decode steps use ncclAllGather instead of peer stores
  *   FLB_FUSE_QUANT=1  also do the step that follows attention (launchAttnQuantizedTransposeKernel,
  *                     open_decoder.cu:245-246) inside the call; the caller then skips its own launch:
@@ -100,7 +102,29 @@ static inline void flb_open_decoder_fill_params(flb_attn_params *ap, int batch_s
     ap->softmax_scale = 1.0f / sqrtf((float)size_per_head_);
     ap->scratch = scratch;
     ap->scratch_bytes = scratch_bytes;
-    ap->scratch_zeroed = 0;
+    /* The decode kernel leaves its arrival counters at zero, so only the first decode call after something else
+     * has used the scratch (a prefill call stages fp16 tiles there, the mask check writes its head) needs them
+     * cleared.  Every later decode call skips the memset and may start early: the kernel in front of it on the
+     * stream is the V projection, and the cache rows it fetches before griddepcontrol.wait were written by
+     * earlier attention calls.  FLB_EARLY_START=0 keeps a memset and an ordinary launch per call. */
+    {
+        static const void *clean_scratch = NULL;
+        static int early = -1;
+#ifdef FLB_OPEN_DECODER_NO_EARLY_START /* for builds in which other code may write the scratch between calls */
+        early = 0;
+#endif
+        if (early < 0) early = flb_open_decoder_env_int("FLB_EARLY_START", 1);
+        if (seq_len > 1 || !early) {
+            clean_scratch = NULL;
+            ap->scratch_zeroed = 0;
+        } else if (clean_scratch != scratch) {
+            clean_scratch = scratch;
+            ap->scratch_zeroed = 0;
+        } else {
+            ap->scratch_zeroed = 1;
+            ap->early_start = 1;
+        }
+    }
     if (flb_open_decoder_fused_quant()) {
         ap->out_q8 = attn_q8;
         ap->out_q8_scale = attn_q8_scale;

@@ -201,6 +201,8 @@ def build(name: str, ref_root: str) -> str:
     if name in ("flb", "mix", "tp"):
         pkg = os.path.join(ROOT, "fasterllama_b200")
         cmd += ["-L", pkg, "-lflb_attn", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../fasterllama_b200"]
+    if name == "mix":
+        cmd += ["-DFLB_OPEN_DECODER_NO_EARLY_START"]  # the reference's own section shares the scratch buffers there
     if name == "tp":
         import torch  # the NCCL this process will already have loaded: link against the same library
         nccl_dir = os.path.join(os.path.dirname(os.path.dirname(torch.__file__)), "nvidia", "nccl")

@@ -217,3 +217,62 @@ def test_early_start_calls_back_to_back(cuda_device):
         outs[early] = [c.arrays["out"].clone() for c, _ in sets] + [c.arrays["k_cache"].clone() for c, _ in sets]
     for a, b in zip(outs[False], outs[True]):
         assert torch.equal(a, b)
+
+
+def test_config4_fp16_13b_full_size_properties(cuda_device):
+    """fp16, batch 64, 40 heads x 128, lengths uniform in [2048, 4096], seed 3 — full size (5.4 GB of cache drawn
+    on the GPU).  The oracle checks a sample of (batch, head) units; size-independent properties cover the rest:
+    every output is finite, a contiguous shard of the units run alone gives the same bits as inside the full
+    batch, and a second call on the same buffers repeats the first."""
+    import torch
+
+    B, H, T = 64, 40, 4097
+    lens = W.draw_lengths(3, B, 2048, 4096)
+    case = W.device_case("config4", 3, B, H, T, lens, device=cuda_device)
+    a = case.arrays
+    A.decode(case.params())
+    torch.cuda.synchronize()
+    assert A.scratch_status(a["scratch"]) == 0
+    out = a["out"].clone()
+    assert torch.isfinite(out.float()).all()
+
+    # sampled units against the host oracle (each on its own [1, 1, T, d] slab)
+    rng = np.random.default_rng(4)
+    for b, h in zip(rng.integers(0, B, 6), rng.integers(0, H, 6)):
+        b, h = int(b), int(h)
+        one = {
+            "q": a["q"][b:b + 1, :, h:h + 1].cpu().numpy(), "k": a["k"][b:b + 1, :, h:h + 1].cpu().numpy(),
+            "v": a["v"][b:b + 1, :, h:h + 1].cpu().numpy(),
+            "k_cache": a["k_cache"][b:b + 1, h:h + 1].cpu().numpy(), "v_cache": a["v_cache"][b:b + 1, h:h + 1].cpu().numpy(),
+            "out": np.zeros((1, 1, 1, 128), dtype=np.float16), "freq_cis": a["freq_cis"].cpu().numpy(),
+            "past_lens": np.array([lens[b]], dtype=np.int32),
+        }
+        # the cache row the call appended is an output: the oracle gets the slab as it was before (row cleared)
+        one["k_cache"][0, 0, lens[b]] = 0
+        one["v_cache"][0, 0, lens[b]] = 0
+        unit = W.Case(name=f"c4-unit-{b}-{h}", B=1, H=1, S=1, T=T, start_pos=0, arrays=one, rope_add_past=case.rope_add_past,
+                      mask_mode=case.mask_mode, max_past_len=int(lens[b]))
+        orc = run_oracle(unit)
+        assert_abs_close(out[b, h].float().cpu().numpy(), orc["out"][0, 0].astype(np.float32), FP16_ABS, f"unit ({b},{h})")
+        k_new, k_want = a["k_cache"][b, h, lens[b]].float().cpu().numpy(), orc["k_cache"][0, 0, lens[b]].astype(np.float32)
+        assert np.abs(k_new - k_want).max() <= 2e-3 * max(1.0, np.abs(k_want).max())  # rotated, rounded to fp16
+        assert np.array_equal(a["v_cache"][b, h, lens[b]].float().cpu().numpy(), orc["v_cache"][0, 0, lens[b]].astype(np.float32))
+
+    # a second call repeats the first (counters were left at zero, the appended row is rewritten with the same bits)
+    A.decode(case.params())
+    torch.cuda.synchronize()
+    assert torch.equal(out, a["out"])
+
+    # one eighth of the batch alone (what one of 8 GPUs would run): same bits
+    sl = slice(8, 16)
+    part = dict(a)
+    for n in ("q", "k", "v", "k_cache", "v_cache"):
+        part[n] = a[n][sl].contiguous()
+    part["out"] = torch.zeros_like(a["out"][sl])
+    part["past_lens"] = a["past_lens"][sl].contiguous()
+    part["scratch"] = torch.zeros(A.workspace_bytes(8, H, T), dtype=torch.uint8, device=cuda_device)
+    sub = W.Case(name="c4-shard", B=8, H=H, S=1, T=T, start_pos=0, arrays=part, rope_add_past=case.rope_add_past,
+                 mask_mode=case.mask_mode, max_past_len=case.max_past_len)
+    A.decode(sub.params())
+    torch.cuda.synchronize()
+    assert torch.equal(part["out"], out[sl])
