@@ -14,17 +14,23 @@
 //    copies of Q (and of K,V when the cache is fp32) for the tensor cores.
 //
 // 2. flb_prefill_attn_kernel — flash attention on the 5th-generation tensor cores.  One CTA per
-//    (b,h, 128-query tile); K/V tiles of 128 keys.  Warp roles:
-//      warp 0      TMA producer: Q once, then K_j / V_j boxes (128-byte swizzle) into a 2-stage ring
-//      warp 1      allocates TMEM and issues tcgen05.mma:  S_j = Q.K_j^T  (fp16 x fp16 -> fp32 in TMEM,
-//                  two S buffers)  and  O += P_j.V_j  (P from shared memory, V as an MN-major operand)
+//    (b,h, 128-query tile), two CTAs per SM (112 KB of shared memory, 256 TMEM columns each); K/V tiles of 64
+//    keys.  Warp roles:
+//      warp 0      K producer: TMA boxes (128-byte swizzle) into a 3-stage ring; a stage is free again as
+//                  soon as S_j has been computed.  Its lane 0 also issues Q and the first K/V tiles before
+//                  the CTA has finished setting up.
+//      warp 1      allocates TMEM and issues tcgen05.mma:  S_j = Q.K_j^T  (fp16 x fp16 -> fp32 in TMEM, two
+//                  S buffers, S_{j+1} is issued before P_j is waited for)  and  O += P_j.V_j  (P read from
+//                  TMEM as the A operand, V from shared memory as an MN-major B operand)
 //      warps 2-5   one thread per query row: tcgen05.ld S, scale + mask, online softmax in the log2
-//                  domain, P_j as fp16 into swizzled shared memory; O in TMEM is rescaled only when a
-//                  row's maximum grew by more than 2^8 (exact: the final division uses the same
-//                  reference maximum); epilogue O / l -> global.
+//                  domain, P_j written back as fp16 pairs over the columns S_j came from; O in TMEM is
+//                  rescaled only when a row's maximum grew by more than 2^8 (exact: the final division
+//                  uses the same reference maximum); epilogue O / l staged through the (by then idle)
+//                  K/V rings and written with coalesced 16-byte stores.
+//      warp 6      V producer: 2-stage ring, a stage is free again once O += P_j.V_j has retired.
 //    All hand-offs are mbarriers (TMA transaction counts, tcgen05.commit, thread arrivals); every
 //    wait is bounded by a wall-clock budget and reports through the status word instead of hanging.
-//    Causal modes skip the key tiles above the diagonal.  TMEM: 512 columns (S0, S1, O).
+//    Causal modes skip the key tiles above the diagonal.  TMEM per CTA: S0, S1 (64 columns each), O (128).
 #include "prefill_attn.cuh"
 
 #include "flb_ptx.cuh"
