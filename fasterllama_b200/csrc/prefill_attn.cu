@@ -164,6 +164,10 @@ template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_
     Raw8 rq[R], rk[R], rv[R];
     float4 f0[R], f1[R];
     float as[R];
+    // lets the attention kernel behind it (launched with programmatic stream serialisation) become resident and
+    // set itself up while this kernel drains
+    grid_launch_dependents();
+    if (blockIdx.x == 0 && threadIdx.x < 4) a.status[threadIdx.x] = 0u; // the call's error word starts clean
     // ---- every load first
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -286,7 +290,12 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
     unsigned char *sK = sQ + Q_TILE_BYTES;                        // K_STAGES tiles
     unsigned char *sV = sK + K_STAGES * Cfg::K_TILE_BYTES;        // V_STAGES tiles
     PrefillBarriers *pb = reinterpret_cast<PrefillBarriers *>(sV + V_STAGES * Cfg::K_TILE_BYTES);
+    // Programmatic dependent launch: what follows up to grid_dependency_wait() (barrier set-up, descriptor
+    // prefetch, TMEM allocation) may run while the prologue kernel is still draining; nothing before the wait
+    // reads or writes global memory.
+    grid_launch_dependents();
     if (smem_u32(smem) & 1023u) { // never observed; without it the MMAs would read scrambled tiles
+        grid_dependency_wait();
         if (threadIdx.x == 0) atomicOr(a.status, kErrPrefillAlign);
         return;
     }
@@ -336,6 +345,7 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
+        grid_dependency_wait(); // the staged Q and the K/V rows are the prologue kernel's output
         mbar_arrive_expect_tx(&pb->q_full, Q_TILE_BYTES);
         tma_load_3d(sQ, &tmQ, 0, q0, bh, &pb->q_full);
         tma_load_3d(sQ + Q_TILE_BYTES / 2, &tmQ, 64, q0, bh, &pb->q_full);
@@ -357,6 +367,7 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    grid_dependency_wait(); // every thread: the mask, the output and the status word are touched from here on
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&pb->tmem_base);
     const uint32_t tS[2] = {tmem, tmem + (uint32_t)BN};
     const uint32_t tO = tmem + 2u * BN;
@@ -725,23 +736,40 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     }
     if (!ok) return FLB_ERR_LAUNCH;
 
-    if (cudaMemsetAsync(sc, 0, 256, stream) != cudaSuccess) return FLB_ERR_LAUNCH;
+    // The attention kernel is launched with programmatic stream serialisation: its CTAs set themselves up
+    // (barriers, descriptors, TMEM) while the prologue drains and wait for it before they touch memory.  The
+    // prologue clears the status word itself, so no memset node sits between the two.
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = stream;
+    cfg.attrs = pdl;
+    cfg.numAttrs = 1;
     const size_t pro_blocks = (size_t)B * H * ((S + 16 * kRowsPerThread - 1) / (16 * kRowsPerThread));
+    cfg.numAttrs = 0; // the prologue itself is launched the ordinary way (measured: starting it early costs 25 us)
+    cfg.gridDim = dim3((unsigned)pro_blocks);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    cudaError_t le;
     if (a.input_mode == 0)
-        flb_prefill_prologue_kernel<0><<<(unsigned)pro_blocks, 256, 0, stream>>>(a);
+        le = cudaLaunchKernelEx(&cfg, flb_prefill_prologue_kernel<0>, a);
     else if (a.input_mode == 1)
-        flb_prefill_prologue_kernel<1><<<(unsigned)pro_blocks, 256, 0, stream>>>(a);
+        le = cudaLaunchKernelEx(&cfg, flb_prefill_prologue_kernel<1>, a);
     else
-        flb_prefill_prologue_kernel<2><<<(unsigned)pro_blocks, 256, 0, stream>>>(a);
-    if (cudaGetLastError() != cudaSuccess) return FLB_ERR_LAUNCH;
+        le = cudaLaunchKernelEx(&cfg, flb_prefill_prologue_kernel<2>, a);
+    if (le != cudaSuccess) return FLB_ERR_LAUNCH;
 
     static_assert(sizeof(PrefillBarriers) <= 256, "barrier block must fit its slot");
     constexpr size_t smem = PrefillCfg<BN>::SMEM;
     if (cudaFuncSetAttribute(flb_prefill_attn_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return FLB_ERR_LAUNCH;
     const int nq = (S + BM - 1) / BM;
-    flb_prefill_attn_kernel<BN><<<(unsigned)(B * H * nq), NUM_THREADS, smem, stream>>>(tmQ, tmK, tmV, a);
-    if (cudaGetLastError() != cudaSuccess) return FLB_ERR_LAUNCH;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3((unsigned)(B * H * nq));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    if (cudaLaunchKernelEx(&cfg, flb_prefill_attn_kernel<BN>, tmQ, tmK, tmV, a) != cudaSuccess) return FLB_ERR_LAUNCH;
     if (p->out_q8) {
         flb_attn_quant_transpose_kernel<<<dim3((unsigned)S, (unsigned)B), 128, 0, stream>>>((const float *)p->out, p->out_q8,
                                                                                            p->out_q8_scale, H, S);
