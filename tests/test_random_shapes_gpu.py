@@ -33,6 +33,40 @@ def test_random_decode(cuda_device, seed):
     assert np.array_equal(cuda["v_cache"], orc["v_cache"].astype(np.float32))
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_random_decode_early_start(cuda_device, seed):
+    """The same kind of draw with zeroed scratch, programmatic dependent launch and three calls in a row."""
+    import torch
+
+    rng = np.random.default_rng(5000 + seed)
+    B, H = int(rng.integers(1, 6)), int(rng.integers(1, 10))
+    T = int(rng.integers(2, 1400))
+    per_seq = bool(rng.integers(0, 2))
+    past = rng.integers(0, T, size=B).astype(np.int32) if per_seq else int(rng.integers(0, T))
+    in_dtype = ["int32", "float32", "float16"][int(rng.integers(0, 3))]
+    cache = ["float32", "float16"][int(rng.integers(0, 2))]
+    case = W.host_case(f"rnd-early-{seed}", 6000 + seed, B, H, T, past=past, in_dtype=in_dtype, cache_dtype=cache, out_dtype="float32",
+                       rope=["past", "reference", "none"][int(rng.integers(0, 3))], mask_mode=MASKS[int(rng.integers(0, 4))],
+                       split_len=int(rng.choice([0, 64, 256])))
+    orc = run_oracle(case)
+    dev = W.to_device(case, cuda_device)
+    dev["scratch"].zero_()
+    case.scratch_zeroed = True
+    case.early_start = True
+    p = case.params(dev)
+    assert p.early_start == 1 and p.scratch_zeroed == 1
+    for _ in range(3):
+        A.decode(p)
+    torch.cuda.synchronize()
+    assert A.scratch_status(dev["scratch"]) == 0
+    got = dev["out"].float().cpu().numpy()
+    if cache == "float16":
+        assert_abs_close(got, orc["out"].astype(np.float32), FP16_ABS, case.name)
+    else:
+        assert_fp32_close(got, orc["out"], what=case.name)
+    assert np.array_equal(dev["v_cache"].float().cpu().numpy(), orc["v_cache"].astype(np.float32))
+
+
 @pytest.mark.parametrize("seed", range(10))
 def test_random_prefill(cuda_device, seed):
     rng = np.random.default_rng(3000 + seed)
