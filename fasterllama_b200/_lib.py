@@ -90,6 +90,10 @@ class FlbPeerExchange(C.Structure):
         ("bytes", C.c_size_t),
         ("status", C.c_void_p),
         ("timeout_ms", C.c_uint),
+        ("out_q8", C.c_void_p),
+        ("out_q8_scale", C.c_void_p),
+        ("q8_rows", C.c_int),
+        ("q8_row_elems", C.c_int),
     ]
 
 
@@ -108,6 +112,7 @@ EXPORTS = {
     "flb_attn_scratch_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint), C.c_void_p]),
     "flb_attn_decode_static_scratch": (C.c_int, [_PP, C.c_void_p]),
     "flb_attn_peer_exchange": (C.c_int, [C.POINTER(FlbPeerExchange), C.c_void_p]),
+    "flb_attn_quantize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
 }
 
 _lib = None

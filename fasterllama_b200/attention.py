@@ -183,8 +183,16 @@ def decode_static_scratch(p: FlbAttnParams, stream=None) -> None:
     _lib.check(_lib.load_library().flb_attn_decode_static_scratch(C.byref(p), _stream_handle(stream)))
 
 
+def quantize(attn, q8, scale, stream=None) -> None:
+    """The reference's attention-output quantisation as a call of its own: attn fp32 [B,H,S,d] -> q8 int8 [B,S,H*d],
+    scale fp32 [B*S]."""
+    B, H, S, d = (int(v) for v in attn.shape)
+    _lib.check(_lib.load_library().flb_attn_quantize(attn.data_ptr(), q8.data_ptr(), scale.data_ptr(), B, H, S, d, _stream_handle(stream)))
+
+
 def peer_exchange(*, rank: int, size: int, epoch: int, flags_local: int, flags_peer, recv: int = 0, dst: int = 0,
-                  nbytes: int = 0, status: int = 0, timeout_ms: int = 0, stream=None) -> None:
+                  nbytes: int = 0, status: int = 0, timeout_ms: int = 0, out_q8: int = 0, out_q8_scale: int = 0,
+                  q8_rows: int = 0, q8_row_elems: int = 0, stream=None) -> None:
     """The hand-shake that follows a pushing decode call (see `flb_peer_exchange`): all pointers are device
     addresses; `flags_peer[r]` is rank r's flag array as mapped into this process."""
     x = _lib.FlbPeerExchange()
@@ -195,6 +203,8 @@ def peer_exchange(*, rank: int, size: int, epoch: int, flags_local: int, flags_p
     x.recv, x.dst, x.bytes = (int(recv) or None), (int(dst) or None), int(nbytes)
     x.status = int(status) or None
     x.timeout_ms = int(timeout_ms)
+    x.out_q8, x.out_q8_scale = (int(out_q8) or None), (int(out_q8_scale) or None)
+    x.q8_rows, x.q8_row_elems = int(q8_rows), int(q8_row_elems)
     _lib.check(_lib.load_library().flb_attn_peer_exchange(C.byref(x), _stream_handle(stream)))
 
 

@@ -222,6 +222,15 @@ int flb_attn_forward(const flb_attn_params *p, void *cuda_stream) {
     return (p->seq_len > 1) ? flb_attn_prefill(p, cuda_stream) : flb_attn_decode(p, cuda_stream);
 }
 
+int flb_attn_quantize(const float *attn, int8_t *q8, float *scale, int batch_size, int head_num, int seq_len, int size_per_head,
+                      void *cuda_stream) {
+    if (!attn || !q8 || !scale) return FLB_ERR_NULL_POINTER;
+    if (batch_size <= 0 || head_num <= 0 || seq_len <= 0) return FLB_ERR_BAD_SHAPE;
+    if (size_per_head != flb::kHeadDim) return FLB_ERR_UNSUPPORTED;
+    if (batch_size > 65535) return FLB_ERR_TOO_LARGE; // grid.y
+    return flb::launch_quantize(attn, q8, scale, batch_size, head_num, seq_len, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int flb_attn_scratch_status(const void *scratch, unsigned *status_out, void *cuda_stream) {
     if (!scratch || !status_out) return FLB_ERR_NULL_POINTER;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);

@@ -778,4 +778,9 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     return FLB_OK;
 }
 
+int launch_quantize(const float *attn, int8_t *q8, float *scale, int B, int H, int S, cudaStream_t stream) {
+    flb_attn_quant_transpose_kernel<<<dim3((unsigned)S, (unsigned)B), 128, 0, stream>>>(attn, q8, scale, H, S);
+    return cudaGetLastError() == cudaSuccess ? FLB_OK : FLB_ERR_LAUNCH;
+}
+
 } // namespace flb

@@ -17,4 +17,7 @@ inline size_t prefill_scratch_bytes(int B, int H, int S) {
 // Launches prologue + attention on `stream`; returns a flb_status.
 int launch_prefill(const flb_attn_params *p, cudaStream_t stream);
 
+// The reference's attention-output quantisation + transpose on a [B,H,S,128] fp32 tensor (one block per token row).
+int launch_quantize(const float *attn, int8_t *q8, float *scale, int B, int H, int S, cudaStream_t stream);
+
 } // namespace flb

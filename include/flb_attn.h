@@ -197,6 +197,15 @@ typedef struct flb_peer_exchange {
     size_t bytes;                         /* multiple of 16                                     */
     unsigned *status;                     /* device word, error bits are OR-ed in               */
     unsigned timeout_ms;                  /* 0 = default (1000)                                 */
+    /* Optional: after the wait, also do the reference's next step on what was received —
+     * launchAttnQuantizedTransposeKernel for seq_len == 1 (decoder_kernels.cu:1179-1255): recv is read as
+     * q8_rows rows of q8_row_elems fp32 values ([B, H*d]); per row absmax (floor -1e9f), out_q8_scale[row]
+     * = absmax / 127, out_q8[row][i] = cvt.rni.sat.s8(x * 127.0f / absmax).  Both NULL = off.  With it,
+     * dst may be NULL: nobody needs the fp32 rows any more. */
+    int8_t *out_q8;
+    float *out_q8_scale;
+    int q8_rows;
+    int q8_row_elems;                     /* multiple of 4                                      */
 } flb_peer_exchange;
 
 #define FLB_STATUS_PEER_WAIT 0x100u
@@ -263,6 +272,14 @@ int flb_attn_scratch_status(const void *scratch, unsigned *status_out, void *cud
  *     other; keep them on one stream.  The status word read by flb_attn_scratch_status() lives in
  *     the block and is not reachable through this entry point. */
 int flb_attn_decode_static_scratch(const flb_attn_params *p, void *cuda_stream);
+
+/* The reference's attention-output quantisation as a call of its own (launchAttnQuantizedTransposeKernel,
+ * fasterLlama/cuda/decoder_kernels.cu:1179-1300, called at open_decoder.cu:245): attn fp32 [B,H,S,d] ->
+ * q8 int8 [B,S,H*d] + scale fp32 [B*S] (absmax over all heads of a token row / 127, floor -1e9f).  The
+ * fused forms (flb_attn_params::out_q8, flb_peer_exchange::out_q8) do the same arithmetic; this entry is
+ * for callers that assemble the [B,H,S,d] tensor themselves, e.g. after an all-gather.  d must be 128. */
+int flb_attn_quantize(const float *attn, int8_t *q8, float *scale, int batch_size, int head_num, int seq_len,
+                      int size_per_head, void *cuda_stream);
 
 /* Signal + bounded wait + copy described at flb_peer_exchange.  One small kernel; no host
  * synchronisation.  No counterpart in the reference. */

@@ -267,15 +267,16 @@ static inline void flb_open_decoder_attention_tp(int batch_size_, int head_num_,
                                                  const float *k_weight_scale, const float *v_weight_scale,
                                                  const float *freq_cis, const float *attn_mask, float *key_cache_,
                                                  float *value_cache_, float *query_out_buf_, float *qk_buf_, float *qkv_buf_,
-                                                 cudaStream_t stream) {
+                                                 int8_t *attn_q8, float *attn_q8_scale, cudaStream_t stream) {
     const int g = flb_tp_state.size, r = flb_tp_state.rank;
+    const int fused = flb_open_decoder_fused_quant() && attn_q8 && attn_q8_scale; /* FLB_FUSE_QUANT=1: see the header comment */
     const int h_local = head_num_ / g;
     const size_t col0 = (size_t)r * h_local * size_per_head_;
     if (g == 1) {
         flb_open_decoder_attention(batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos, query_buf_,
                                    key_buf_, value_buf_, from_tensor_scale_buf_, q_weight_scale, k_weight_scale, v_weight_scale,
-                                   freq_cis, attn_mask, key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, NULL, NULL, stream);
-        (void)max_prompt_len_;
+                                   freq_cis, attn_mask, key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, attn_q8, attn_q8_scale,
+                                   stream);
         return;
     }
     /* local heads: q/k/v are [B*S, h_local*d].  query_out_buf_, key_out_buf_, value_out_fp_buf_ are three equal
@@ -312,8 +313,18 @@ static inline void flb_open_decoder_attention_tp(int batch_size_, int head_num_,
             x.flags_local = (unsigned *)s->push_base[r];
             for (int i = 0; i < g; ++i) x.flags_peer[i] = (unsigned *)s->push_base[i];
             x.recv = s->push_base[r] + slot_off;
-            x.dst = qkv_buf_;
             x.bytes = row_bytes;
+            if (fused) {
+                /* the received rows are quantised where they landed (the reference's next kernel, which the caller
+                 * then skips); nobody reads the fp32 rows after that, so they are not copied into qkv_buf_ */
+                x.dst = NULL;
+                x.out_q8 = attn_q8;
+                x.out_q8_scale = attn_q8_scale;
+                x.q8_rows = batch_size_;
+                x.q8_row_elems = head_num_ * size_per_head_;
+            } else {
+                x.dst = qkv_buf_;
+            }
             x.status = (unsigned *)(s->push_base[r] + 128); /* sticky: read it with flb_tp_push_status() */
             x.timeout_ms = 2000;
             flb_open_decoder_check(flb_attn_peer_exchange(&x, stream), "flb_attn_peer_exchange", __LINE__);
@@ -334,6 +345,9 @@ static inline void flb_open_decoder_attention_tp(int batch_size_, int head_num_,
         printf("NCCL Error:\n    File:   %s\n    Line:   %d\n    %s\n", __FILE__, __LINE__, ncclGetErrorString(nr));
         exit(1);
     }
+    if (fused) /* the caller skips its own quantisation launch: do it on the gathered tensor */
+        flb_open_decoder_check(flb_attn_quantize(qkv_buf_, attn_q8, attn_q8_scale, batch_size_, head_num_, seq_len, size_per_head_, stream),
+                               "flb_attn_quantize", __LINE__);
 }
 #endif /* FLB_WITH_NCCL */
 

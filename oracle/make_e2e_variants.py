@@ -162,9 +162,10 @@ def patch_tp(src: str) -> None:
                                           query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
                                           param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
                                           param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
-                                          key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, param_.stream);"""
+                                          key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, from_tensor_int8_buf_, from_tensor_scale_buf_,
+                                          param_.stream);"""
     lines[s:e] = call.split("\n")
-    text = "\n".join(lines)
+    text = patch_quant_call("\n".join(lines))
     text = text.replace('#include "open_decoder.h"', '#include "open_decoder.h"\n#include "flb_open_decoder.h"', 1)
     open(p, "w").write(text)
 

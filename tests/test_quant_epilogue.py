@@ -85,3 +85,44 @@ def test_quantisation_needs_fp32_output_and_both_pointers():
     c2.arrays["scratch"] = np.zeros(A.workspace_bytes(2, 4, 64), dtype=np.uint8)
     c2.arrays["out_q8"] = np.zeros((2, 1, 512), dtype=np.int8)
     assert A.validate(c2.params()) == _lib.FLB_ERR_NULL_POINTER
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(3, 8, 1), (2, 5, 37), (1, 32, 1)])
+def test_standalone_quantize_call(cuda_device, shape):
+    """flb_attn_quantize on a tensor the caller assembled itself (e.g. after an all-gather): bit-exact against the
+    oracle, including an all-zero row (a fully masked query)."""
+    import torch
+    B, H, S = shape
+    g = torch.Generator(device="cuda")
+    g.manual_seed(9)
+    attn = torch.randn((B, H, S, 128), generator=g, device="cuda") * 3.0
+    attn[0, :, 0] = 0.0
+    q8 = torch.full((B, S, H * 128), 99, dtype=torch.int8, device="cuda")
+    sc = torch.full((B * S,), float("nan"), device="cuda")
+    A.quantize(attn, q8, sc)
+    torch.cuda.synchronize()
+    want_q8, want_sc = oracle.attn_quantize(attn.cpu().numpy())
+    assert np.array_equal(sc.cpu().numpy(), want_sc)
+    assert np.array_equal(q8.cpu().numpy(), want_q8)
+
+
+@pytest.mark.gpu
+def test_exchange_kernel_quantises_what_it_received(cuda_device):
+    """The exchange step of the head-split decode layer with the quantisation folded in (one rank: no waiting):
+    rows [B, H*d] in the receive slot -> int8 codes + scales, no fp32 copy."""
+    import torch
+    B, H = 5, 12
+    g = torch.Generator(device="cuda")
+    g.manual_seed(10)
+    recv = torch.randn((B, H, 1, 128), generator=g, device="cuda") * 2.0
+    recv[3] = 0.0
+    q8 = torch.full((B, 1, H * 128), 99, dtype=torch.int8, device="cuda")
+    sc = torch.full((B,), float("nan"), device="cuda")
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    A.peer_exchange(rank=0, size=1, epoch=1, flags_local=flags.data_ptr(), flags_peer=[0], recv=recv.data_ptr(), nbytes=recv.numel() * 4,
+                    out_q8=q8.data_ptr(), out_q8_scale=sc.data_ptr(), q8_rows=B, q8_row_elems=H * 128)
+    torch.cuda.synchronize()
+    want_q8, want_sc = oracle.attn_quantize(recv.cpu().numpy())
+    assert np.array_equal(sc.cpu().numpy(), want_sc)
+    assert np.array_equal(q8.cpu().numpy(), want_q8)

@@ -155,14 +155,17 @@ E2E_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.skipif(not all(os.path.exists(os.path.join(E2E_DIR, f"libe2e_{v}.so")) for v in ("flb", "tp")),
                     reason="end-to-end libraries not built")
+@pytest.mark.parametrize("fuse_quant", [False, True])
 @pytest.mark.parametrize("exchange", ["peer stores", "nccl"])
 @pytest.mark.parametrize("config", ["small", "medium"])
-def test_tensor_parallel_generation_matches_one_gpu(cuda_device, tmp_path, config, exchange):
+def test_tensor_parallel_generation_matches_one_gpu(cuda_device, tmp_path, config, exchange, fuse_quant):
     """The reference's DecodingSampling with the tensor-parallel layer (Q/K/V projections on a column slice,
     head-sharded attention, one exchange of head outputs per layer: NCCL all-gather in prefill; in decode either
     peer stores from the decode kernel + flag hand-shake, or NCCL again) on two GPUs samples exactly the
     ids of the one-GPU adaptor run: int32 projections are exact under the column split, each head's
-    attention is bit-identical wherever it runs, and the exchange is a copy."""
+    attention is bit-identical wherever it runs, and the exchange is a copy.  With fuse_quant the layer's next
+    step (attention-output quantisation) is done by the exchange kernel on the rows it received (decode) or by
+    flb_attn_quantize on the gathered tensor (prefill, NCCL decode) instead of by the reference's kernel."""
     import json
     import subprocess
 
@@ -176,7 +179,7 @@ def test_tensor_parallel_generation_matches_one_gpu(cuda_device, tmp_path, confi
         port = s.getsockname()[1]
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
                         "--master-port", str(port), e2e, "--variant", "tp", "--config", config, "--out", two]
-                       + (["--no-push"] if exchange == "nccl" else []),
+                       + (["--no-push"] if exchange == "nccl" else []) + (["--fuse-quant"] if fuse_quant else []),
                        capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
     line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1]
