@@ -44,8 +44,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32
 }
 
 // ---- 1-D bulk copy global -> shared, completion on an mbarrier -------------------------
-// dst, src 16-byte aligned, bytes a multiple of 16.  No multicast: the destination is this
-// CTA's own shared memory.
+// dst, src 16-byte aligned, bytes a multiple of 16.  The destination is this CTA's own shared
+// memory and nobody else's.
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                      smem_u32(dst_smem)),
@@ -78,7 +78,7 @@ __device__ __forceinline__ float ex2(float x) {
 
 namespace flb {
 
-// Tiled TMA load of one box of a rank-3 tensor map into this CTA's shared memory (no multicast).
+// Tiled TMA load of one box of a rank-3 tensor map into this CTA's own shared memory.
 // c0 is the innermost coordinate: c0 * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_3d(void *dst_smem, const CUtensorMap *tm, int c0, int c1, int c2, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
