@@ -62,3 +62,26 @@ def test_free_running_generation_small(cuda_device, tmp_path, mask):
     assert match >= 0.5, f"only {match:.2f} of the sampled ids agree with the reference"
     # the prompt is teacher-forced by both, so the very first sampled token depends on prefill only
     assert (ra["ids"][:, 0] == rb["ids"][:, 0]).mean() >= 0.5
+
+
+def test_adaptor_switches_do_not_change_the_ids(cuda_device, tmp_path):
+    """Fused attention-output quantisation (FLB_FUSE_QUANT=1) and ordinary launches with a counter memset per call
+    (FLB_EARLY_START=0) are different ways to issue the same arithmetic: the sampled ids must not move."""
+    base, fused, plain = (str(tmp_path / n) for n in ("base.npz", "fused.npz", "plain.npz"))
+    _run("flb", "medium", base)
+    _run("flb", "medium", fused, extra=("--fuse-quant",))
+    _run("flb", "medium", plain, env={"FLB_EARLY_START": "0"})
+    a, b, c = np.load(base), np.load(fused), np.load(plain)
+    assert np.array_equal(a["ids"], b["ids"]) and np.array_equal(a["seq_len"], b["seq_len"])
+    assert np.array_equal(a["ids"], c["ids"]) and np.array_equal(a["seq_len"], c["seq_len"])
+
+
+def test_fp16_cache_generation_runs_and_is_deterministic(cuda_device, tmp_path):
+    """FLB_CACHE_F16=1 keeps the caches as halves inside the caller's float slabs: a different (coarser) cache
+    format, so ids may differ from the fp32-cache run, but the run is deterministic and complete."""
+    a, b = (str(tmp_path / n) for n in ("h1.npz", "h2.npz"))
+    _run("flb", "small", a, extra=("--cache-f16",))
+    _run("flb", "small", b, extra=("--cache-f16",))
+    ra, rb = np.load(a), np.load(b)
+    assert np.array_equal(ra["ids"], rb["ids"]) and np.array_equal(ra["seq_len"], rb["seq_len"])
+    assert int(ra["seq_len"].max()) > 0
