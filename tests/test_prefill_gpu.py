@@ -112,3 +112,12 @@ def test_config3_shape_sampled_heads(cuda_device):
                              for k, v in case.arrays.items()})
         o = run_oracle(sub)
         assert_abs_close(r["out"][b, h], o["out"][0, 0].astype(np.float32), PREFILL_ABS, f"config3 unit ({b},{h})")
+
+
+@pytest.mark.parametrize("S,mask_mode", [(1500, A.FLB_MASK_CAUSAL_INCLUSIVE), (2049, A.FLB_MASK_CAUSAL_STRICT), (1300, A.FLB_MASK_NONE)])
+def test_long_prompts(cuda_device, S, mask_mode):
+    """Prompts well beyond the benchmark's 1024 tokens (up to 33 key tiles per query tile, ragged last tiles):
+    the barrier phases, the ring indices and the lazy rescaling have run many times over by the end."""
+    case = W.host_case(f"long-S{S}", 900 + S, 1, 1, S + 7, S=S, past=0, in_dtype="float16", cache_dtype="float16",
+                       out_dtype="float32", rope="past", mask_mode=mask_mode)
+    _check(case, run_cuda(case), run_oracle(case, f16_operands=True), cache16=True)
