@@ -276,3 +276,14 @@ def test_config4_fp16_13b_full_size_properties(cuda_device):
     A.decode(sub.params())
     torch.cuda.synchronize()
     assert torch.equal(part["out"], out[sl])
+
+
+@pytest.mark.parametrize("cache_dtype", ["float32", "float16"])
+def test_cache_at_the_reference_softmax_limit(cuda_device, cache_dtype):
+    """12288 keys is where the reference's softmax kernel runs out of shared memory (4 bytes per key); here it is
+    24 partitions of 512 rows per (batch, head) unit and one merge.  Ragged neighbours: 12287, 12288 and 1 keys."""
+    lens = np.array([12286, 12287, 0], dtype=np.int32)
+    fp16 = cache_dtype == "float16"
+    case = W.host_case("long-cache", 88, 3, 2, 12288, past=lens, in_dtype="float16" if fp16 else "float32", cache_dtype=cache_dtype,
+                       out_dtype="float32")
+    _check(case, run_cuda(case), run_oracle(case), fp16=fp16)
