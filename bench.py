@@ -225,6 +225,19 @@ def run_ours(args, rank, world, local):
     for c, _ in sets:
         assert A.scratch_status(c.arrays["scratch"]) == 0, "a decode kernel reported an error status"
 
+    # spread of a single call: 200 launches timed one by one (each between its own pair of events, the stream
+    # idle before it), so these include the launch latency that back-to-back calls hide
+    singles = []
+    es = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]
+    for i, (a0, a1) in enumerate(es):
+        a0.record(stream)
+        step(i)
+        a1.record(stream)
+        stream.synchronize()
+    singles = sorted(a0.elapsed_time(a1) * 1e3 for a0, a1 in es)
+    spread = {"p10": round(singles[20], 2), "p50": round(singles[100], 2), "p90": round(singles[180], 2),
+              "what": "one call at a time, stream idle before each (us)"}
+
     # ---- end to end: host q/k/v in, output back on the host, every step --------------------------
     host_in = [c.arrays["qkv"].cpu().pin_memory() for c, _ in sets]
     host_out = torch.empty_like(sets[0][0].arrays["out"], device="cpu").pin_memory()
@@ -291,6 +304,7 @@ def run_ours(args, rank, world, local):
         "pct_of_8TBps": round(100 * value / world / 8000.0, 2),
         "bytes_per_step_per_gpu": bytes_step,
         "gpu_launches": args.steps,
+        "single_call_us": spread,
         "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": round(t_e2e / args.steps * 1e3, 5), "tokens_per_s": round(tokens_step * args.steps / t_e2e, 1),
                 "host_buffers": ("pinned host q/k/v/out handed to the call; the kernel reads and writes them over PCIe, host waits for each step"
