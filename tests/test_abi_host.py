@@ -124,3 +124,24 @@ def test_status_strings():
     seen = {lib.flb_status_string(s) for s in range(0, -10, -1)}
     assert len(seen) == 10 and all(seen)
     assert lib.flb_status_string(-77) == b"unknown status"
+
+
+def test_exchange_and_quantize_argument_checks_need_no_gpu():
+    """Both calls answer bad arguments before they touch the CUDA runtime."""
+    lib = _lib.load_library()
+    x = _lib.FlbPeerExchange()
+    assert lib.flb_attn_peer_exchange(None, None) == _lib.FLB_ERR_NULL_POINTER
+    assert lib.flb_attn_peer_exchange(C.byref(x), None) == _lib.FLB_ERR_NULL_POINTER  # no flag words
+    x.flags_local = 4096
+    x.rank, x.size, x.epoch = 0, 9, 1
+    assert lib.flb_attn_peer_exchange(C.byref(x), None) == _lib.FLB_ERR_BAD_SHAPE  # more ranks than FLB_MAX_PEERS
+    x.size, x.epoch = 2, 0
+    assert lib.flb_attn_peer_exchange(C.byref(x), None) == _lib.FLB_ERR_BAD_SHAPE  # epochs start at 1
+    x.epoch = 1
+    x.out_q8 = 4096  # codes without a place for the scales
+    assert lib.flb_attn_peer_exchange(C.byref(x), None) == _lib.FLB_ERR_NULL_POINTER
+    x.out_q8 = None
+    assert lib.flb_attn_peer_exchange(C.byref(x), None) == _lib.FLB_ERR_NULL_POINTER  # rank 1's flag words missing
+    assert lib.flb_attn_quantize(None, None, None, 1, 1, 1, 128, None) == _lib.FLB_ERR_NULL_POINTER
+    assert lib.flb_attn_quantize(4096, 4096, 4096, 1, 1, 1, 64, None) == _lib.FLB_ERR_UNSUPPORTED
+    assert lib.flb_attn_quantize(4096, 4096, 4096, 0, 1, 1, 128, None) == _lib.FLB_ERR_BAD_SHAPE
