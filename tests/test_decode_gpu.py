@@ -287,3 +287,38 @@ def test_cache_at_the_reference_softmax_limit(cuda_device, cache_dtype):
     case = W.host_case("long-cache", 88, 3, 2, 12288, past=lens, in_dtype="float16" if fp16 else "float32", cache_dtype=cache_dtype,
                        out_dtype="float32")
     _check(case, run_cuda(case), run_oracle(case), fp16=fp16)
+
+
+@pytest.mark.parametrize("early", [False, True])
+def test_decode_calls_can_be_captured_in_a_graph(cuda_device, early):
+    """The call allocates nothing and never synchronises, so a run of decode calls can be recorded once and
+    replayed as one graph launch (ordinary launches and early-start launches alike); replays repeat the bits."""
+    import torch
+
+    lens = W.draw_lengths(9, 4, 100, 900)
+    sets = []
+    for j in range(2):
+        c = W.device_case("graph", 70 + j, 4, 8, 901, lens, device=cuda_device)
+        c.scratch_zeroed = True
+        c.early_start = early
+        sets.append((c, c.params()))
+    for c, p in sets:
+        A.decode(p)
+    torch.cuda.synchronize()
+    want = [c.arrays["out"].clone() for c, _ in sets]
+    for c, _ in sets:
+        c.arrays["out"].zero_()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for i in range(6):
+                A.decode(sets[i % 2][1], torch.cuda.current_stream())
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert all(A.scratch_status(c.arrays["scratch"]) == 0 for c, _ in sets)
+    for (c, _), w in zip(sets, want):
+        assert torch.equal(c.arrays["out"], w)
