@@ -195,7 +195,7 @@ def run_ours(args, rank, world, local):
     for j in range(NBUF):
         c = W.device_case(f"{args.workload}-{j}", seed + 7919 * j + 104729 * rank, B, H, T, lens, device=dev)
         c.scratch_zeroed = True  # device_case hands over zeroed scratch; the kernel leaves it zeroed
-        c.early_start = not args.no_early_start
+        c.early_start = 0 if args.no_early_start else args.early_start
         # q, k, v as three views of one buffer, so that the end-to-end leg moves them with one host->device copy
         c.arrays["qkv"] = torch.stack([c.arrays[n] for n in ("q", "k", "v")]).contiguous()
         c.arrays["q"], c.arrays["k"], c.arrays["v"] = c.arrays["qkv"][0], c.arrays["qkv"][1], c.arrays["qkv"][2]
@@ -294,8 +294,10 @@ def run_ours(args, rank, world, local):
         "config": {
             "workload": desc, "per_gpu_batch": B, "heads": H, "head_dim": 128, "cache_rows_total": int(lens.sum()),
             "total_len": T, "split_len": 512,
-            "launch": ("programmatic dependent launch: a call's CTAs may become resident and fetch their first cache tiles while the previous call drains; inputs, scratch and outputs are touched only after it has completed"
-                       if not args.no_early_start else "ordinary stream launches"),
+            "launch": ("ordinary stream launches" if args.no_early_start else
+                       "programmatic dependent launch, level 1: a call's CTAs may become resident and fetch their first cache tiles while the previous call drains; inputs, scratch and outputs are touched only after it has completed"
+                       if args.early_start == 1 else
+                       "programmatic dependent launch, level 2: a call's CTAs may become resident while the previous call drains and stream the cache against q and k (which, as in the decoder layer, are final before the kernel in front starts); the new token's v, the cache append, scratch and outputs are touched only after the previous call has completed"),
             "l2": f"{NBUF} distinct input sets rotated ({NBUF * bytes_step / 1e6:.0f} MB > 126 MB L2), no flush kernel in the timed region",
             "sharding": ("one batch split over the ranks by contiguous (batch, head) ranges, no collective" if strong
                          else "every rank runs its own batch of this shape (independent (batch, head) units), no collective"),
@@ -617,6 +619,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + list(PREFILL_WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the host-oracle baseline leg")
+    ap.add_argument("--early-start", type=int, default=2, choices=[1, 2],
+                    help="level of the programmatic dependent launch (flb_attn_params.early_start): 1 = only cache tiles are fetched before the previous call has completed, 2 = the whole pass over the cache")
     ap.add_argument("--no-early-start", action="store_true",
                     help="launch every decode call the ordinary way (default: programmatic dependent launch, a call may fetch its first cache tiles while the previous one drains)")
     ap.add_argument("--e2e-mode", default="mapped", choices=["mapped", "copies"],

@@ -81,7 +81,7 @@ def make_params(
     out_head_total: int = 0,
     out_head_offset: int = 0,
     out_dtype: str | None = None,
-    early_start: bool = False,
+    early_start: int = 0,
 ) -> FlbAttnParams:
     """Fills a `flb_attn_params`.  Shapes: q/k/v [B,S,H,d]; caches [B,H,T,d]; out [B,H,S,d];
     past_lens int32 [B]; freq_cis float32 [rows,d]; attn_mask float32 [*, mask_row_stride]."""
@@ -128,7 +128,7 @@ def make_params(
     p.scratch_bytes = int(scratch.numel() * scratch.element_size()) if hasattr(scratch, "numel") else (int(scratch.nbytes) if scratch is not None else 0)
     p.scratch_zeroed = int(bool(scratch_zeroed))
     p.split_len = int(split_len)
-    p.early_start = int(bool(early_start))
+    p.early_start = int(early_start)  # 0 off, 1 or 2: see flb_attn_params.early_start
     p.out_q8, p.out_q8_scale = _ptr(out_q8), _ptr(out_q8_scale)
     # keep the tensors alive as long as the block
     p._keep = (q, k, v, k_cache, v_cache, out, scratch, past_lens, act_scale, q_w_scale, k_w_scale, v_w_scale, freq_cis, attn_mask, out_q8, out_q8_scale)

@@ -230,18 +230,19 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
     } else {
         // ---------------- compute warps ------------------------------------------------------
         const int tid = threadIdx.x; // < NC
-        // everything below reads this step's inputs or writes global memory: the previous kernel must be done
-        if (a.early_start) grid_dependency_wait();
-        if (bad_len && tid == 0 && split == 0) atomicOr(a.status, 4u);
-        // -- the new token: dequantise, rotate, append (a2, a3, a4 of the reference in one place)
+        // Early start, level 1: q, k and v all come from the kernel in front -> wait before any of them is read.
+        // Level 2: the caller has promised that q and k (with their scales) were final before that kernel started
+        // (in the decoder layer it is the V projection, the Q and K projections ran before it), so the whole
+        // streaming pass over the cache runs first and only the new token's v, the cache append and the
+        // result/scratch writes wait (after the loop below).
+        if (a.early_start == 1) grid_dependency_wait();
+        float krot_keep = 0.f; // the new token's rotated k, appended to the cache after the streaming pass
+        // -- the new token: dequantise, rotate (a2 of the reference); its v and the append (a3, a4) follow the loop
         {
-            float qraw = 0.f, kraw = 0.f, vraw = 0.f;
+            float qraw = 0.f, kraw = 0.f;
             if (tid < D) {
                 qraw = load_input(a, a.q, a.q_w_scale, unit, b, h, tid);
-                if (is_last) {
-                    kraw = load_input(a, a.k, a.k_w_scale, unit, b, h, tid);
-                    vraw = load_input(a, a.v, a.v_w_scale, unit, b, h, tid);
-                }
+                if (is_last) kraw = load_input(a, a.k, a.k_w_scale, unit, b, h, tid);
             }
             float qrot = qraw, krot = kraw;
             if (a.freq_cis) {
@@ -267,10 +268,7 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
                 q_s[tid] = qs;
                 if (is_last) {
                     const float kr = CacheIO<CacheT>::round(krot);
-                    vnew = CacheIO<CacheT>::round(vraw);
-                    const size_t c = ((size_t)unit * a.T + past) * D + tid;
-                    CacheIO<CacheT>::store((CacheT *)a.k_cache + c, krot);
-                    CacheIO<CacheT>::store((CacheT *)a.v_cache + c, vraw);
+                    krot_keep = krot;
                     part = qs * kr;
                 }
             }
@@ -376,6 +374,19 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
+        }
+
+        // -- from here on the kernel writes global memory and reads the new token's v: the kernel in front of
+        //    this one must have completed (a no-op unless the launch was an early-start one)
+        if (a.early_start == 2) grid_dependency_wait();
+        if (bad_len && tid == 0 && split == 0) atomicOr(a.status, 4u);
+        if (is_last && tid < D) {
+            // a3, a4 of the reference: dequantise v, round k and v to the cache type, append row `past`
+            const float vraw = load_input(a, a.v, a.v_w_scale, unit, b, h, tid);
+            vnew = CacheIO<CacheT>::round(vraw);
+            const size_t cidx = ((size_t)unit * a.T + past) * D + tid;
+            CacheIO<CacheT>::store((CacheT *)a.k_cache + cidx, krot_keep);
+            CacheIO<CacheT>::store((CacheT *)a.v_cache + cidx, vraw);
         }
 
         if (RPI == 2) {

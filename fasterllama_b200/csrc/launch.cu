@@ -48,6 +48,7 @@ int check_common(const flb_attn_params *p) {
     if (p->split_len < 0 || (p->split_len % 32) != 0) return FLB_ERR_BAD_SHAPE;
     if (!p->q || !p->k || !p->v || !p->k_cache || !p->v_cache) return FLB_ERR_NULL_POINTER;
     if (p->n_out_peers < 0 || p->n_out_peers > FLB_MAX_PEERS) return FLB_ERR_BAD_SHAPE;
+    if (p->early_start < 0 || p->early_start > 2) return FLB_ERR_BAD_ENUM;
     if (p->n_out_peers == 0) {
         if (!p->out) return FLB_ERR_NULL_POINTER;
         if (!aligned16(p->out)) return FLB_ERR_MISALIGNED;
@@ -201,7 +202,7 @@ int flb_attn_decode(const flb_attn_params *p, void *cuda_stream) {
     a.n_out_peers = p->n_out_peers;
     a.out_head_total = p->out_head_total;
     a.out_head_offset = p->out_head_offset;
-    a.early_start = (p->early_start != 0 && p->scratch_zeroed != 0) ? 1 : 0;
+    a.early_start = (p->scratch_zeroed != 0) ? p->early_start : 0;
     a.part_ml = reinterpret_cast<float *>(sc + l.ml_off);
     a.part_o = reinterpret_cast<float *>(sc + l.o_off);
 

@@ -58,7 +58,7 @@ class Case:
     split_len: int = 0
     max_past_len: int = 0
     scratch_zeroed: bool = False
-    early_start: bool = False  # decode: programmatic dependent launch (see flb_attn_params.early_start)
+    early_start: int = 0  # decode: programmatic dependent launch, level 0 / 1 / 2 (see flb_attn_params.early_start)
     meta: dict[str, Any] = field(default_factory=dict)
 
     def params(self, arrays: dict[str, Any] | None = None, out_peers=None, out_head_total: int = 0, out_head_offset: int = 0):

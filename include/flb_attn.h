@@ -167,13 +167,19 @@ typedef struct flb_attn_params {
     int out_head_offset;
 
     /* Decode only, optional: early_start != 0 launches the kernel with programmatic stream
-     * serialisation.  Its CTAs may then become resident, and fetch their first cache tiles, while the
-     * previous kernel on the stream is still draining; q, k, v, the scales, the scratch and every
-     * output are touched only after that kernel has completed (griddepcontrol.wait).  The caller
-     * promises that the cache rows below each sequence's length and past_lens were final BEFORE the
-     * previous kernel on the stream started (true in the decoder layer: the kernel in front is the
-     * QKV projection).  Needs scratch_zeroed != 0 (a memset in front would serialise anyway); ignored
-     * otherwise.  A decode kernel launched this way also lets the next such call start early. */
+     * serialisation.  Its CTAs may then become resident while the previous kernel on the stream is still
+     * draining; what they do before that kernel has completed (griddepcontrol.wait) depends on the level:
+     *   1  fetch their first cache tiles.  Promise: the cache rows below each sequence's length and
+     *      past_lens were final BEFORE the previous kernel on the stream started.
+     *   2  in addition read q and k, rotate them and run the whole pass over the cached rows.  Promise,
+     *      on top of level 1: q, k, act_scale, the weight scales and freq_cis were final before the
+     *      previous kernel started — only v may still be in flight.  True in the decoder layer, where the
+     *      kernel in front is the V projection and the Q and K projections ran before it
+     *      (open_decoder.cu:105-136).
+     * At both levels the new token's v, the cache append, the scratch and every output are touched only
+     * after the previous kernel has completed, and the results are bit-identical to an ordinary launch.
+     * Needs scratch_zeroed != 0 (a memset in front would serialise anyway); ignored otherwise.  A decode
+     * kernel launched this way also lets the next such call start early. */
     int early_start;
 } flb_attn_params;
 

@@ -104,9 +104,11 @@ static inline void flb_open_decoder_fill_params(flb_attn_params *ap, int batch_s
     ap->scratch_bytes = scratch_bytes;
     /* The decode kernel leaves its arrival counters at zero, so only the first decode call after something else
      * has used the scratch (a prefill call stages fp16 tiles there, the mask check writes its head) needs them
-     * cleared.  Every later decode call skips the memset and may start early: the kernel in front of it on the
-     * stream is the V projection, and the cache rows it fetches before griddepcontrol.wait were written by
-     * earlier attention calls.  FLB_EARLY_START=0 keeps a memset and an ordinary launch per call. */
+     * cleared.  Every later decode call skips the memset and may start early (level 2): the kernel in front of it
+     * on the stream is the V projection, so q and k (Q and K projections, open_decoder.cu:105-125), the
+     * activation scales and the cache rows written by earlier attention calls are final, and the whole pass over
+     * the cache can run while that GEMM drains; only the new token's v, the append and the outputs wait for it.
+     * FLB_EARLY_START=0 keeps a memset and an ordinary launch per call. */
     {
         static const void *clean_scratch = NULL;
         static int early = -1;
@@ -122,7 +124,7 @@ static inline void flb_open_decoder_fill_params(flb_attn_params *ap, int batch_s
             ap->scratch_zeroed = 0;
         } else {
             ap->scratch_zeroed = 1;
-            ap->early_start = 1;
+            ap->early_start = 2; /* q and k come from the two projections before the one in front of this call */
         }
     }
     if (flb_open_decoder_fused_quant()) {

@@ -193,15 +193,15 @@ def test_pinned_host_inputs_and_output(cuda_device, in_dtype, cache_dtype, out_d
 
 
 def test_early_start_calls_back_to_back(cuda_device):
-    """Programmatic dependent launch: a chain of decode calls that may each start while the one before drains
-    gives the same bits as ordinary launches — on rotating buffer sets and on one set reused by every call."""
+    """Programmatic dependent launch (both levels): a chain of decode calls that may each start while the one before
+    drains gives the same bits as ordinary launches — on rotating buffer sets and on one set reused by every call."""
     import torch
 
     from fasterllama_b200 import workloads as W2
 
     lens = W2.draw_lengths(5, 6, 200, 1500)
     outs = {}
-    for early in (False, True):
+    for early in (0, 1, 2):
         sets = []
         for j in range(3):
             c = W2.device_case("early", 50 + j, 6, 8, 1501, lens, device=cuda_device)
@@ -214,9 +214,11 @@ def test_early_start_calls_back_to_back(cuda_device):
             A.decode(sets[0][1])  # the same buffers, scratch and counters in consecutive launches
         torch.cuda.synchronize()
         assert all(A.scratch_status(c.arrays["scratch"]) == 0 for c, _ in sets)
-        outs[early] = [c.arrays["out"].clone() for c, _ in sets] + [c.arrays["k_cache"].clone() for c, _ in sets]
-    for a, b in zip(outs[False], outs[True]):
-        assert torch.equal(a, b)
+        outs[early] = ([c.arrays["out"].clone() for c, _ in sets] + [c.arrays["k_cache"].clone() for c, _ in sets]
+                       + [c.arrays["v_cache"].clone() for c, _ in sets])
+    for level in (1, 2):
+        for a, b in zip(outs[0], outs[level]):
+            assert torch.equal(a, b)
 
 
 def test_config4_fp16_13b_full_size_properties(cuda_device):
@@ -289,7 +291,7 @@ def test_cache_at_the_reference_softmax_limit(cuda_device, cache_dtype):
     _check(case, run_cuda(case), run_oracle(case), fp16=fp16)
 
 
-@pytest.mark.parametrize("early", [False, True])
+@pytest.mark.parametrize("early", [0, 1, 2])
 def test_decode_calls_can_be_captured_in_a_graph(cuda_device, early):
     """The call allocates nothing and never synchronises, so a run of decode calls can be recorded once and
     replayed as one graph launch (ordinary launches and early-start launches alike); replays repeat the bits."""

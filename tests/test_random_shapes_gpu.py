@@ -52,9 +52,9 @@ def test_random_decode_early_start(cuda_device, seed):
     dev = W.to_device(case, cuda_device)
     dev["scratch"].zero_()
     case.scratch_zeroed = True
-    case.early_start = True
+    case.early_start = 1 + seed % 2
     p = case.params(dev)
-    assert p.early_start == 1 and p.scratch_zeroed == 1
+    assert p.early_start == 1 + seed % 2 and p.scratch_zeroed == 1
     for _ in range(3):
         A.decode(p)
     torch.cuda.synchronize()
