@@ -92,6 +92,10 @@ def test_validate_accepts_a_good_block_and_names_each_fault():
     assert A.validate(p) == _lib.FLB_ERR_NULL_POINTER
     p = c.params(); p.n_out_peers = 9
     assert A.validate(p) == _lib.FLB_ERR_BAD_SHAPE
+    p = c.params(); p.early_start = 3  # levels are 0, 1, 2
+    assert A.validate(p) == _lib.FLB_ERR_BAD_ENUM
+    p = c.params(); p.early_start = 2
+    assert A.validate(p) == _lib.FLB_OK
     assert _lib.load_library().flb_attn_validate(None) == _lib.FLB_ERR_NULL_POINTER
 
 
