@@ -204,7 +204,17 @@ def run_ours(args, rank, world, local):
     tokens_step = WORKLOADS[args.workload][0] if strong else B * world  # sequences advanced per step, all ranks
     stream = torch.cuda.current_stream()
 
+    # Back-to-back calls with early start level 2 overlap each other's ramp and drain, so partitions no longer
+    # have to be small to shorten a call's tail: one partition per (batch, head) unit (no partial results, no merge)
+    # is fastest there.  Isolated calls (the single-call and end-to-end legs below) keep the library's default.
+    import dataclasses
+    chain_split = args.split_len if args.split_len else (2048 if (args.early_start == 2 and not args.no_early_start) else 512)
+    chain = [dataclasses.replace(c, split_len=chain_split).params() for c, _ in sets]
+
     def step(i):
+        A.decode(chain[i % NBUF], stream)
+
+    def single(i):
         A.decode(sets[i % NBUF][1], stream)
 
     for i in range(max(args.warmup, 3)):
@@ -231,7 +241,7 @@ def run_ours(args, rank, world, local):
     es = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]
     for i, (a0, a1) in enumerate(es):
         a0.record(stream)
-        step(i)
+        single(i)
         a1.record(stream)
         stream.synchronize()
     singles = sorted(a0.elapsed_time(a1) * 1e3 for a0, a1 in es)
@@ -293,7 +303,7 @@ def run_ours(args, rank, world, local):
         "vs_baseline": None, "dtype": "f16 storage, f32 arithmetic", "data": "synthetic",
         "config": {
             "workload": desc, "per_gpu_batch": B, "heads": H, "head_dim": 128, "cache_rows_total": int(lens.sum()),
-            "total_len": T, "split_len": 512,
+            "total_len": T, "split_len": chain_split, "split_len_single_call_and_e2e": 512,
             "launch": ("ordinary stream launches" if args.no_early_start else
                        "programmatic dependent launch, level 1: a call's CTAs may become resident and fetch their first cache tiles while the previous call drains; inputs, scratch and outputs are touched only after it has completed"
                        if args.early_start == 1 else
@@ -619,6 +629,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + list(PREFILL_WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the host-oracle baseline leg")
+    ap.add_argument("--split-len", type=int, default=0,
+                    help="rows per split-KV partition in the back-to-back leg (0: 2048 with early start level 2, else the library's 512)")
     ap.add_argument("--early-start", type=int, default=2, choices=[1, 2],
                     help="level of the programmatic dependent launch (flb_attn_params.early_start): 1 = only cache tiles are fetched before the previous call has completed, 2 = the whole pass over the cache")
     ap.add_argument("--no-early-start", action="store_true",
