@@ -643,6 +643,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a GPU: there is no CPU path to measure")
     torch.cuda.set_device(local)
+    launched = world
     if args.impl == "reference":
         world = 1  # rank 0 alone runs the reference arm; the other ranks leave without work
     if world > 1:
@@ -651,7 +652,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     try:
         if args.impl == "reference":
-            run_reference(args, rank, world, local)
+            run_reference(args, rank, launched, local)
         else:
             from fasterllama_b200 import _lib
 
