@@ -215,6 +215,10 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
             for (int t = 0; t < ntiles; ++t) {
                 const int s = t % STAGES;
                 const uint32_t use = (uint32_t)(t / STAGES);
+                // Level 1: the compute warps sit in griddepcontrol.wait until the kernel in front has completed and
+                // free no stage before that, so once the ring is full this lane waits for the same event instead
+                // of spending its bounded spin on a stage that cannot become free yet.
+                if (a.early_start == 1 && t == STAGES) grid_dependency_wait();
                 if (!mbar_wait(&empty[s], (use & 1u) ^ 1u)) {
                     atomicOr(a.status, kErrProducerWait);
                     break;

@@ -13,24 +13,30 @@
 //    transpose [B,S,H,d] -> [B,H,S,d], append k,v to the caches (rows 0..S-1) and leave fp16
 //    copies of Q (and of K,V when the cache is fp32) for the tensor cores.
 //
-// 2. flb_prefill_attn_kernel — flash attention on the 5th-generation tensor cores.  One CTA per
-//    (b,h, 128-query tile), two CTAs per SM (112 KB of shared memory, 256 TMEM columns each); K/V tiles of 64
-//    keys.  Warp roles:
-//      warp 0      K producer: TMA boxes (128-byte swizzle) into a 3-stage ring; a stage is free again as
-//                  soon as S_j has been computed.  Its lane 0 also issues Q and the first K/V tiles before
-//                  the CTA has finished setting up.
-//      warp 1      allocates TMEM and issues tcgen05.mma:  S_j = Q.K_j^T  (fp16 x fp16 -> fp32 in TMEM, two
-//                  S buffers, S_{j+1} is issued before P_j is waited for)  and  O += P_j.V_j  (P read from
-//                  TMEM as the A operand, V from shared memory as an MN-major B operand)
-//      warps 2-5   one thread per query row: tcgen05.ld S, scale + mask, online softmax in the log2
-//                  domain, P_j written back as fp16 pairs over the columns S_j came from; O in TMEM is
-//                  rescaled only when a row's maximum grew by more than 2^8 (exact: the final division
-//                  uses the same reference maximum); epilogue O / l staged through the (by then idle)
-//                  K/V rings and written with coalesced 16-byte stores.
-//      warp 6      V producer: 2-stage ring, a stage is free again once O += P_j.V_j has retired.
+// 2. flb_prefill_attn_kernel — flash attention on the 5th-generation tensor cores, one persistent CTA of 16
+//    warps per SM.  A work item is 256 query rows of one (b,h) (two 128-row tiles); items are handed out through
+//    an atomic counter, heavy (late) query blocks first, in groups of heads whose K/V stay in L2.  K/V tiles
+//    hold 128 keys.  TMEM (512 columns): S0, S1 (fp32 scores of the two query tiles; P overwrites them as fp16
+//    pairs) and O0, O1 (fp32 accumulators).  Warp roles:
+//      warp 0      work scheduler + K loader: TMA boxes (128-byte swizzle) into a ring; a stage is free again
+//                  once both query tiles' S = Q.K^T over it have been computed
+//      warp 1      allocates TMEM and issues tcgen05.mma in the order PV0_j, S0_{j+1}, PV1_j, S1_{j+1}: while
+//                  one query tile's scores go through the softmax warps the tensor pipe works on the other's.
+//                  S is an SS form (both operands in shared memory, 128 x 128 x 16 per instruction), P.V reads
+//                  P from TMEM as the A operand and V from shared memory as an MN-major B operand.  At an item
+//                  boundary the next item's first S takes the place of S_{j+1}: the pipe never drains.
+//      warp 2      V loader (its own ring: a stage is free again once both P.V products have retired)
+//      warp 3      Q loader: a query tile's buffer is refilled as soon as its last S of the item has retired
+//      warps 4-7   softmax of query tile 0, one thread per row: two passes over the 128 scores in TMEM (row
+//      warps 8-11  maximum, then P = 2^(x - m) and the row sum), 32 columns in flight while 32 are worked on;
+//      (tile 1)    the keys 0..63 half of P is handed to the tensor core before the second half is computed; O is
+//                  rescaled only when a row's maximum grew by more than 2^8 (exact: the final division uses
+//                  the same reference maximum); a share of the exponentials runs on the FMA pipe
+//      warps 12-15 epilogue: O_t / l from TMEM to global memory while the other warps are on the next item
 //    All hand-offs are mbarriers (TMA transaction counts, tcgen05.commit, thread arrivals); every
 //    wait is bounded by a wall-clock budget and reports through the status word instead of hanging.
-//    Causal modes skip the key tiles above the diagonal.  TMEM per CTA: S0, S1 (64 columns each), O (128).
+//    Causal modes skip the key tiles above the diagonal.  No multicast, no cluster: the same code runs in the
+//    head-split layer on several GPUs.
 #include "prefill_attn.cuh"
 
 #include "flb_ptx.cuh"
@@ -42,14 +48,27 @@ namespace flb {
 namespace {
 
 constexpr int D = 128;       // head dimension
-constexpr int BM = 128;      // query rows per CTA
-constexpr int K_STAGES = 3;              // K ring: a stage is free again once S_j = Q.K_j^T has completed
-constexpr int V_STAGES = 2;              // V ring: a stage is free again once O += P_j.V_j has completed
-constexpr int Q_TILE_BYTES = BM * D * 2; // 128 x 128 fp16 = 32 KB, two [128 x 64] swizzled blocks
-constexpr int NUM_THREADS = 224;         // warps: 0 Q+K loads, 1 MMA, 2-5 softmax, 6 V loads
-constexpr int kKeysPerTile = 64;         // BN: 112 KB of shared memory and 256 TMEM columns per CTA -> 2 CTAs per SM
+constexpr int BM = 128;      // query rows per tile (two tiles per work item)
+constexpr int BN = 128;      // keys per K/V tile
+constexpr int TILE_BYTES = 128 * D * 2;   // any 128-row fp16 tile (Q, K or V): 32 KB = two [128 x 64] swizzled blocks
+constexpr int HALF_BYTES = TILE_BYTES / 2;
+#ifndef FLB_PF_K_STAGES
+#define FLB_PF_K_STAGES 3
+#endif
+#ifndef FLB_PF_V_STAGES
+#define FLB_PF_V_STAGES 2
+#endif
+#ifndef FLB_PF_EMUL
+#define FLB_PF_EMUL 4
+#endif
+constexpr int K_STAGES = FLB_PF_K_STAGES; // K ring: a stage is free again once S = Q.K^T over it has completed
+constexpr int V_STAGES = FLB_PF_V_STAGES; // V ring: a stage is free again once O += P.V over it has completed
+constexpr int kExpOnFmaEvery = FLB_PF_EMUL; // every n-th exponential of a row on the FMA pipe (0 = none)
+constexpr int NUM_THREADS = 512;          // warps: 0 scheduler + K loads, 1 MMA, 2 V loads, 3 Q loads, 4-11 softmax, 12-15 epilogue
+constexpr uint32_t TMEM_COLS = 512;       // S0, S1, O0, O1: 128 columns each
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f; // log2 domain: P stays below 2^8, exact in fp16 range
+constexpr int kWorkCounterWord = 4;       // word of the status header the work scheduler counts in (cleared by the prologue)
 
 enum : unsigned { kErrPrefillWait = 8u, kErrPrefillAlign = 16u };
 
@@ -167,7 +186,7 @@ template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_
     // lets the attention kernel behind it (launched with programmatic stream serialisation) become resident and
     // set itself up while this kernel drains
     grid_launch_dependents();
-    if (blockIdx.x == 0 && threadIdx.x < 4) a.status[threadIdx.x] = 0u; // the call's error word starts clean
+    if (blockIdx.x == 0 && threadIdx.x < 8) a.status[threadIdx.x] = 0u; // the call's error word and the work counter start clean
     // ---- every load first
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -224,24 +243,28 @@ template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_
 // ------------------------------------------------------------------------------------------------
 // attention
 // ------------------------------------------------------------------------------------------------
+constexpr int SCHED_DEPTH = 4;        // work items the scheduler may publish ahead
+constexpr int kSchedConsumers = 15;   // V loader, Q loader, MMA issuer, 8 softmax warps, 4 epilogue warps
+constexpr int kHeadsPerGroup = 32;    // work list: groups of this many (b,h) units, heavy query blocks first inside a group
+
 struct __align__(8) PrefillBarriers {
-    uint64_t q_full;
+    uint64_t q_full[2], q_empty[2];   // per query tile of the item
     uint64_t k_full[K_STAGES], k_empty[K_STAGES];
     uint64_t v_full[V_STAGES], v_empty[V_STAGES];
-    uint64_t s_full[2];  // S_j = Q.K_j^T landed in TMEM buffer j%2
-    uint64_t p_full[2];  // P_j written over S_j's columns by the 128 softmax threads (and O rescaled if needed)
-    uint64_t pv_done;    // O += P_j.V_j completed (one phase per tile)
-    uint64_t o_full;     // last P.V completed
+    uint64_t s_full[2];               // S_t = Q_t.K_j^T landed in TMEM
+    uint64_t p_full[2][2];            // P_t written over S_t's columns: keys 0..63, keys 64..127 (128 arrivals each)
+    uint64_t pv_done[2];              // O_t += P_t.V_j retired (one phase per tile)
+    uint64_t o_full[2], o_empty[2];   // last P.V of an item retired / the epilogue has read O_t out of TMEM
+    uint64_t l_full[2], l_empty[2];   // row sums of an item in shared memory / read by the epilogue
+    uint64_t sched_full[SCHED_DEPTH], sched_empty[SCHED_DEPTH];
+    int sched_bh[SCHED_DEPTH], sched_qb[SCHED_DEPTH]; // the published items; bh < 0 = no more work
     uint32_t tmem_base;
     int abort_flag;
 };
-
-template <int BN> struct PrefillCfg {
-    static constexpr int K_TILE_BYTES = BN * D * 2;     // K or V tile: BN keys x 128 dims fp16
-    static constexpr int K_HALF = K_TILE_BYTES / 2;     // one [BN x 64] swizzled block
-    static constexpr uint32_t TMEM_COLS = (BN == 64) ? 256u : 512u; // S0, S1 (BN columns each) + O (128)
-    static constexpr size_t SMEM = (size_t)Q_TILE_BYTES + (K_STAGES + V_STAGES) * K_TILE_BYTES + 256;
-};
+constexpr int kBarrierSlot = 512;
+constexpr size_t kPrefillSmem = (size_t)(2 + K_STAGES + V_STAGES) * TILE_BYTES + 2 * BM * sizeof(float) + kBarrierSlot;
+static_assert(sizeof(PrefillBarriers) <= kBarrierSlot, "barrier block must fit its slot");
+static_assert(kPrefillSmem <= 232448, "exceeds the 227 KB a CTA may use");
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
@@ -265,35 +288,85 @@ __device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, Prefill
     return false;
 }
 
-#ifdef FLB_CTATRACE
-// debug build only: four time stamps + SM id per CTA (softmax warp 2, lane 0), after the one-CTA time line's area
-#define CT(k) do { if (warp == 2 && lane == 0) ct[blockIdx.x * 8 + (k)] = globaltimer_ns(); } while (0)
-#else
-#define CT(k) do { } while (0)
-#endif
-#ifdef FLB_TIMELINE
-// debug build only: per-role time stamps of one CTA, written into the (unused with an fp16 cache) K staging area
-#define TL(role, tile, k) do { if (tl_on) tl[((role) * 64 + (tile)) * 4 + (k)] = globaltimer_ns(); } while (0)
-#else
-#define TL(role, tile, k) do { } while (0)
-#endif
+// A work item is 256 query rows of one (b,h): two 128-row tiles, each with its own S/P and O columns in TMEM.
+struct ItemGeom {
+    int q0[2];   // first query row of tile t
+    int n[2];    // key tiles tile t attends over (0 = the tile lies beyond the prompt)
+    int nmax;
+};
+__device__ __forceinline__ ItemGeom item_geom(int qb, int S, bool causal) {
+    ItemGeom g;
+    const int n_all = (S + BN - 1) / BN;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        g.q0[t] = qb * (2 * BM) + t * BM;
+        // causal modes skip the key tiles above the diagonal: tile t ends at key q0 + 127
+        g.n[t] = (g.q0[t] < S) ? (causal ? min(n_all, g.q0[t] / BN + 1) : n_all) : 0;
+    }
+    g.nmax = max(g.n[0], g.n[1]);
+    return g;
+}
 
-template <int BN>
-__global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
+// Next published item for a consumer role (`count` = items this role has taken so far).  Single-thread roles
+// release the slot themselves; warp roles read on every lane and let lane 0 release after a __syncwarp().
+__device__ __forceinline__ bool sched_read(PrefillBarriers *pb, unsigned *status, uint32_t count, int &bh, int &qb) {
+    const uint32_t slot = count % SCHED_DEPTH;
+    if (!wait_bar(&pb->sched_full[slot], (count / SCHED_DEPTH) & 1u, pb, status)) return false;
+    bh = *reinterpret_cast<volatile int *>(&pb->sched_bh[slot]);
+    qb = *reinterpret_cast<volatile int *>(&pb->sched_qb[slot]);
+    return true;
+}
+__device__ __forceinline__ void sched_release(PrefillBarriers *pb, uint32_t count) { mbar_arrive(&pb->sched_empty[count % SCHED_DEPTH]); }
+
+// One 128-key score tile of one query row: row maximum, P = 2^(x - m) written back as fp16 pairs over the columns
+// the scores came from (keys 2c, 2c+1 in column c), row sum.  MODE 0: every key visible, x = s * scale; MODE 1:
+// keys [0, lim) visible (causal diagonal / end of the prompt); MODE 2: additionally the caller's additive mask.
+// EMUL > 0: every EMUL-th exponential is evaluated on the FMA pipe instead of the special-function unit.
+template <int MODE> __device__ __forceinline__ float score_of(uint32_t raw, int idx, int lim, float scale, const float *mrow) {
+    if (MODE == 0) return __uint_as_float(raw);
+    if (MODE == 1) return (idx < lim) ? __uint_as_float(raw) * scale : -INFINITY;
+    return (idx < lim) ? fmaf(__ldg(mrow + idx), kLog2e, __uint_as_float(raw) * scale) : -INFINITY;
+}
+template <int MODE> __device__ __forceinline__ float chunk_max(const uint32_t (&r)[32], int base, int lim, float scale, const float *mrow, float m) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2)
+        m = max3(m, score_of<MODE>(r[i], base + i, lim, scale, mrow), score_of<MODE>(r[i + 1], base + i + 1, lim, scale, mrow));
+    return m;
+}
+template <int MODE, int EMUL>
+__device__ __forceinline__ void chunk_exp(const uint32_t (&r)[32], int base, int lim, float scale, const float *mrow, float neg_m,
+                                          float2 &l2, uint32_t (&packed)[16]) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        float2 y;
+        if (MODE == 0) {
+            y = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), make_float2(scale, scale),
+                           make_float2(neg_m, neg_m));
+        } else {
+            y = __fadd2_rn(make_float2(score_of<MODE>(r[i], base + i, lim, scale, mrow), score_of<MODE>(r[i + 1], base + i + 1, lim, scale, mrow)),
+                           make_float2(neg_m, neg_m));
+        }
+        float2 p;
+        constexpr int E = EMUL > 0 ? EMUL : 1;
+        p.x = (EMUL > 0 && (i % E) == E - 1) ? ex2_fma(y.x) : ex2(y.x);
+        p.y = (EMUL > 0 && ((i + 1) % E) == E - 1) ? ex2_fma(y.y) : ex2(y.y);
+        l2 = __fadd2_rn(l2, p);
+        const __half2 h2 = __floats2half2_rn(p.x, p.y);
+        packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&h2);
+    }
+}
+
+template <int EMUL>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
     flb_prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                            const __grid_constant__ CUtensorMap tmV, const PrefillArgs a) {
-    using Cfg = PrefillCfg<BN>;
-    constexpr int NCH = BN / 32; // 32-column chunks of one score row
+                            const __grid_constant__ CUtensorMap tmV, const PrefillArgs a, const int num_items) {
     // The 128-byte swizzle pattern is a function of address bits [4,10): tiles must start on 1 KB.
     extern __shared__ __align__(1024) unsigned char smem[];
-    unsigned char *sQ = smem;                                     // two [128 x 64] blocks
-    unsigned char *sK = sQ + Q_TILE_BYTES;                        // K_STAGES tiles
-    unsigned char *sV = sK + K_STAGES * Cfg::K_TILE_BYTES;        // V_STAGES tiles
-    PrefillBarriers *pb = reinterpret_cast<PrefillBarriers *>(sV + V_STAGES * Cfg::K_TILE_BYTES);
-    // Programmatic dependent launch: what follows up to grid_dependency_wait() (barrier set-up, descriptor
-    // prefetch, TMEM allocation) may run while the prologue kernel is still draining; nothing before the wait
-    // reads or writes global memory.
-    grid_launch_dependents();
+    unsigned char *sQ = smem;                                  // two query tiles
+    unsigned char *sK = sQ + 2 * TILE_BYTES;                   // K ring
+    unsigned char *sV = sK + K_STAGES * TILE_BYTES;            // V ring
+    float *l_buf = reinterpret_cast<float *>(sV + V_STAGES * TILE_BYTES); // [2][128] row sums of the item being finished
+    PrefillBarriers *pb = reinterpret_cast<PrefillBarriers *>(l_buf + 2 * BM);
     if (smem_u32(smem) & 1023u) { // never observed; without it the MMAs would read scrambled tiles
         grid_dependency_wait();
         if (threadIdx.x == 0) atomicOr(a.status, kErrPrefillAlign);
@@ -301,30 +374,22 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef FLB_TIMELINE
-    const bool tl_on = (blockIdx.x == gridDim.x / 2 + 1) && (lane == 0);
-    uint64_t *tl = reinterpret_cast<uint64_t *>(a.kh);
-    if (tl_on && warp == 0) tl[3 * 64 * 4] = globaltimer_ns();
-#endif
-#ifdef FLB_CTATRACE
-    uint64_t *ct = reinterpret_cast<uint64_t *>(a.kh) + 4096;
-    CT(0);
-    if (warp == 2 && lane == 0) {
-        uint32_t smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        ct[blockIdx.x * 8 + 5] = smid;
-    }
-#endif
-    const int nq = (a.S + BM - 1) / BM;
-    const int bh = blockIdx.x / nq;
-    const int qt = nq - 1 - (int)(blockIdx.x % nq); // heavy (late) query tiles first within a head
-    const int q0 = qt * BM;
     const bool causal = (a.mask_mode == 2 || a.mask_mode == 3);
-    const int n_all = (a.S + BN - 1) / BN;
-    const int n_tiles = causal ? min(n_all, (q0 + BM) / BN) : n_all;
+    const int nqb = (a.S + 2 * BM - 1) / (2 * BM); // 256-row query blocks per (b,h)
 
     if (threadIdx.x == 0) {
-        mbar_init(&pb->q_full, 1);
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&pb->q_full[t], 1);
+            mbar_init(&pb->q_empty[t], 1);
+            mbar_init(&pb->s_full[t], 1);
+            mbar_init(&pb->p_full[t][0], BM);
+            mbar_init(&pb->p_full[t][1], BM);
+            mbar_init(&pb->pv_done[t], 1);
+            mbar_init(&pb->o_full[t], 1);
+            mbar_init(&pb->o_empty[t], BM);
+            mbar_init(&pb->l_full[t], BM);
+            mbar_init(&pb->l_empty[t], BM);
+        }
         for (int s = 0; s < K_STAGES; ++s) {
             mbar_init(&pb->k_full[s], 1);
             mbar_init(&pb->k_empty[s], 1);
@@ -333,71 +398,143 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
             mbar_init(&pb->v_full[s], 1);
             mbar_init(&pb->v_empty[s], 1);
         }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&pb->s_full[s], 1);
-            mbar_init(&pb->p_full[s], 128);
+        for (int s = 0; s < SCHED_DEPTH; ++s) {
+            mbar_init(&pb->sched_full[s], 1);
+            mbar_init(&pb->sched_empty[s], kSchedConsumers);
         }
-        mbar_init(&pb->pv_done, 1);
-        mbar_init(&pb->o_full, 1);
         pb->abort_flag = 0;
         mbar_fence_init();
-        // the first loads leave before the CTA has finished setting up (no stage is in use yet)
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
-        grid_dependency_wait(); // the staged Q and the K/V rows are the prologue kernel's output
-        mbar_arrive_expect_tx(&pb->q_full, Q_TILE_BYTES);
-        tma_load_3d(sQ, &tmQ, 0, q0, bh, &pb->q_full);
-        tma_load_3d(sQ + Q_TILE_BYTES / 2, &tmQ, 64, q0, bh, &pb->q_full);
-        for (int j = 0; j < K_STAGES && j < n_tiles; ++j) {
-            mbar_arrive_expect_tx(&pb->k_full[j], Cfg::K_TILE_BYTES);
-            tma_load_3d(sK + j * Cfg::K_TILE_BYTES, &tmK, 0, j * BN, bh, &pb->k_full[j]);
-            tma_load_3d(sK + j * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmK, 64, j * BN, bh, &pb->k_full[j]);
-        }
-        for (int j = 0; j < V_STAGES && j < n_tiles; ++j) {
-            mbar_arrive_expect_tx(&pb->v_full[j], Cfg::K_TILE_BYTES);
-            tma_load_3d(sV + j * Cfg::K_TILE_BYTES, &tmV, 0, j * BN, bh, &pb->v_full[j]);
-            tma_load_3d(sV + j * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmV, 64, j * BN, bh, &pb->v_full[j]);
-        }
     }
     if (warp == 1) {
-        tmem_alloc(&pb->tmem_base, Cfg::TMEM_COLS);
+        tmem_alloc(&pb->tmem_base, TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    grid_dependency_wait(); // every thread: the mask, the output and the status word are touched from here on
+    // Programmatic dependent launch: everything above ran while the prologue kernel was draining; its output (the
+    // staged Q, the cache rows, the cleared status words and work counter) is touched only from here on.  The
+    // kernel behind this one is let go only after that wait, so "the kernel in front of it has completed" keeps
+    // meaning "everything before that has completed as well".
+    grid_dependency_wait();
+    grid_launch_dependents();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&pb->tmem_base);
     const uint32_t tS[2] = {tmem, tmem + (uint32_t)BN};
-    const uint32_t tO = tmem + 2u * BN;
+    const uint32_t tO[2] = {tmem + 2u * BN, tmem + 2u * BN + (uint32_t)D};
 
     if (warp == 0) {
-        // ======================= TMA producer: the K ring (Q and the first stages left at set-up) ======
+        // ======================= work scheduler + K loader =======================
         if (lane == 0) {
-            for (int j = K_STAGES; j < n_tiles; ++j) {
-                const int s = j % K_STAGES;
-                const uint32_t u = (uint32_t)(j / K_STAGES);
-                TL(0, j, 0);
-                if (!wait_bar(&pb->k_empty[s], (u & 1u) ^ 1u, pb, a.status)) break;
-                TL(0, j, 1);
-                mbar_arrive_expect_tx(&pb->k_full[s], Cfg::K_TILE_BYTES);
-                tma_load_3d(sK + s * Cfg::K_TILE_BYTES, &tmK, 0, j * BN, bh, &pb->k_full[s]);
-                tma_load_3d(sK + s * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmK, 64, j * BN, bh, &pb->k_full[s]);
+            unsigned *counter = a.status + kWorkCounterWord;
+            const int BH = a.B * a.H;
+            const int per_group = kHeadsPerGroup * nqb, full_groups = BH / kHeadsPerGroup;
+            uint32_t published = 0, kt = 0;
+            bool ok = true;
+            // item k of the list -> (b,h) unit and query block: groups of 32 units (their K/V stay in L2 while the
+            // group is worked on), late = heavy query blocks first inside a group
+            auto decode = [&](int k, int &bh, int &qb) {
+                if (k < 0) { bh = -1; qb = 0; return; }
+                const int g = k / per_group;
+                if (g < full_groups) {
+                    const int r = k - g * per_group;
+                    qb = nqb - 1 - r / kHeadsPerGroup;
+                    bh = g * kHeadsPerGroup + r % kHeadsPerGroup;
+                } else {
+                    const int rem = BH - full_groups * kHeadsPerGroup, r = k - full_groups * per_group;
+                    qb = nqb - 1 - r / rem;
+                    bh = full_groups * kHeadsPerGroup + r % rem;
+                }
+            };
+            auto publish = [&](int k) -> bool {
+                const uint32_t slot = published % SCHED_DEPTH;
+                if (!wait_bar(&pb->sched_empty[slot], ((published / SCHED_DEPTH) & 1u) ^ 1u, pb, a.status)) return false;
+                int bh, qb;
+                decode(k, bh, qb);
+                pb->sched_bh[slot] = bh;
+                pb->sched_qb[slot] = qb;
+                mbar_arrive(&pb->sched_full[slot]); // release: the two words above are visible to whoever sees the phase
+                ++published;
+                return true;
+            };
+            // the first gridDim.x items are taken by block index (no round trip before the first load); the rest
+            // through the counter, which the prologue kernel left at zero
+            auto fetch = [&]() -> int {
+                const unsigned k = gridDim.x + atomicAdd(counter, 1u);
+                return k < (unsigned)num_items ? (int)k : -1;
+            };
+            auto load_k = [&](int bh, int j) -> bool {
+                const uint32_t s = kt % K_STAGES;
+                if (!wait_bar(&pb->k_empty[s], ((kt / K_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
+                mbar_arrive_expect_tx(&pb->k_full[s], TILE_BYTES);
+                tma_load_3d(sK + s * TILE_BYTES, &tmK, 0, j * BN, bh, &pb->k_full[s]);
+                tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, 64, j * BN, bh, &pb->k_full[s]);
+                ++kt;
+                return true;
+            };
+            int cur = (int)blockIdx.x; // < num_items: the grid never exceeds the item count
+            ok = publish(cur);
+            while (cur >= 0 && ok) {
+                const int nxt = fetch(); // in flight while the first tile of `cur` is issued
+                int bh, qb;
+                decode(cur, bh, qb);
+                const ItemGeom g = item_geom(qb, a.S, causal);
+                ok = load_k(bh, 0);
+                if (ok) ok = publish(nxt); // one item of look-ahead for the other roles
+                for (int j = 1; j < g.nmax && ok; ++j) ok = load_k(bh, j);
+                cur = nxt;
             }
         }
         __syncwarp();
-    } else if (warp == 6) {
-        // ======================= TMA producer: the V ring =======================
+    } else if (warp == 2) {
+        // ======================= V loader =======================
         if (lane == 0) {
-            for (int j = V_STAGES; j < n_tiles; ++j) {
-                const int s = j % V_STAGES;
-                const uint32_t u = (uint32_t)(j / V_STAGES);
-                if (!wait_bar(&pb->v_empty[s], (u & 1u) ^ 1u, pb, a.status)) break;
-                TL(0, j, 2);
-                mbar_arrive_expect_tx(&pb->v_full[s], Cfg::K_TILE_BYTES);
-                tma_load_3d(sV + s * Cfg::K_TILE_BYTES, &tmV, 0, j * BN, bh, &pb->v_full[s]);
-                tma_load_3d(sV + s * Cfg::K_TILE_BYTES + Cfg::K_HALF, &tmV, 64, j * BN, bh, &pb->v_full[s]);
+            uint32_t taken = 0, vt = 0;
+            for (;;) {
+                int bh, qb;
+                if (!sched_read(pb, a.status, taken, bh, qb)) break;
+                sched_release(pb, taken++);
+                if (bh < 0) break;
+                const ItemGeom g = item_geom(qb, a.S, causal);
+                bool ok = true;
+                for (int j = 0; j < g.nmax && ok; ++j) {
+                    const uint32_t s = vt % V_STAGES;
+                    ok = wait_bar(&pb->v_empty[s], ((vt / V_STAGES) & 1u) ^ 1u, pb, a.status);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&pb->v_full[s], TILE_BYTES);
+                    tma_load_3d(sV + s * TILE_BYTES, &tmV, 0, j * BN, bh, &pb->v_full[s]);
+                    tma_load_3d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, 64, j * BN, bh, &pb->v_full[s]);
+                    ++vt;
+                }
+                if (!ok) break;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 3) {
+        // ======================= Q loader =======================
+        if (lane == 0) {
+            uint32_t taken = 0, cq[2] = {0, 0};
+            for (;;) {
+                int bh, qb;
+                if (!sched_read(pb, a.status, taken, bh, qb)) break;
+                sched_release(pb, taken++);
+                if (bh < 0) break;
+                const ItemGeom g = item_geom(qb, a.S, causal);
+                bool ok = true;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (g.n[t] == 0 || !ok) continue;
+                    // free again once the last S of the previous item on this tile has been computed
+                    ok = wait_bar(&pb->q_empty[t], (cq[t] & 1u) ^ 1u, pb, a.status);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&pb->q_full[t], TILE_BYTES);
+                    tma_load_3d(sQ + t * TILE_BYTES, &tmQ, 0, g.q0[t], bh, &pb->q_full[t]);
+                    tma_load_3d(sQ + t * TILE_BYTES + HALF_BYTES, &tmQ, 64, g.q0[t], bh, &pb->q_full[t]);
+                    ++cq[t];
+                }
+                if (!ok) break;
             }
         }
         __syncwarp();
@@ -406,235 +543,328 @@ __global__ void __launch_bounds__(NUM_THREADS, (BN == 64) ? 2 : 1)
         if (lane == 0) {
             // S = Q.K^T : A (Q) and B (K) both K-major, 128-byte swizzle, 8-row groups 1024 B apart
             constexpr uint32_t idesc_qk = umma_idesc_f16(BM, BN, false, false);
-            // O += P.V  : A (P) from TMEM (fp16 pairs in the columns S_j occupied); B (V) MN-major: 64-dim
-            // blocks K_HALF apart (LBO), 8-key groups 1024 B apart (SBO)
+            // O += P.V  : A (P) from TMEM (fp16 pairs in the columns S came from); B (V) MN-major: the two 64-dim
+            // blocks HALF_BYTES apart (LBO), 8-key groups 1024 B apart (SBO)
             constexpr uint32_t idesc_pv = umma_idesc_f16(BM, D, false, true);
             const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
-            bool ok = wait_bar(&pb->q_full, 0, pb, a.status);
+            uint32_t taken = 0, kt = 0, vt = 0;
+            uint32_t cq[2] = {0, 0}, cp[2] = {0, 0}, ci[2] = {0, 0};
+            bool ok = true;
 
-            // The tensor pipe executes one thread's MMAs in issue order: S_0, S_1, PV_0, S_2, PV_1, ...
-            // so S_{j+2} overwrites TMEM buffer j%2 only after PV_j has read P_j from it.
-            auto issue_s = [&](int j) -> bool {
-                const int s = j & 1, ks = j % K_STAGES;
-                TL(1, j, 0);
-                if (!wait_bar(&pb->k_full[ks], (uint32_t)(j / K_STAGES) & 1u, pb, a.status)) return false;
-                TL(1, j, 1);
+            // The tensor pipe executes this thread's MMAs in issue order: ... PV0_j, S0_{j+1}, PV1_j, S1_{j+1}, ...
+            // so S_t overwrites its TMEM buffer only after the P.V that read P_t from it.
+            auto issue_s = [&](int t, bool first_of_item, bool last_of_item) -> bool {
+                if (first_of_item) {
+                    if (!wait_bar(&pb->q_full[t], cq[t] & 1u, pb, a.status)) return false;
+                    ++cq[t];
+                }
                 tc_fence_after();
+                const uint32_t ks = kt % K_STAGES;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint64_t da = umma_desc_sw128(aQ + (kk >> 2) * (Q_TILE_BYTES / 2) + (kk & 3) * 32, 16, 1024);
-                    const uint64_t db = umma_desc_sw128(aK + ks * Cfg::K_TILE_BYTES + (kk >> 2) * Cfg::K_HALF + (kk & 3) * 32, 16, 1024);
-                    umma_f16_ss(tS[s], da, db, idesc_qk, kk > 0 ? 1u : 0u);
+                    const uint64_t da = umma_desc_sw128(aQ + t * TILE_BYTES + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
+                    const uint64_t db = umma_desc_sw128(aK + ks * TILE_BYTES + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
+                    umma_f16_ss(tS[t], da, db, idesc_qk, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(&pb->s_full[s]);
-                umma_commit(&pb->k_empty[ks]);
+                umma_commit(&pb->s_full[t]);
+                if (last_of_item) umma_commit(&pb->q_empty[t]);
                 return true;
             };
-            if (ok) ok = issue_s(0);
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j & 1;
-                const uint32_t u = (uint32_t)(j >> 1);
-                if (j + 1 < n_tiles) {
-                    ok = issue_s(j + 1);
-                    if (!ok) break;
-                }
-                const int vs = j % V_STAGES;
-                if (!wait_bar(&pb->v_full[vs], (uint32_t)(j / V_STAGES) & 1u, pb, a.status)) { ok = false; break; }
-                TL(1, j, 2);
-                if (!wait_bar(&pb->p_full[s], u & 1u, pb, a.status)) { ok = false; break; }
-                TL(1, j, 3);
-                tc_fence_after();
+            auto wait_k = [&]() -> bool { return wait_bar(&pb->k_full[kt % K_STAGES], (kt / K_STAGES) & 1u, pb, a.status); };
+            auto release_k = [&]() {
+                umma_commit(&pb->k_empty[kt % K_STAGES]);
+                ++kt;
+            };
+
+            int bh, qb;
+            ok = sched_read(pb, a.status, taken, bh, qb);
+            if (ok) sched_release(pb, taken++);
+            bool valid = ok && bh >= 0;
+            ItemGeom g = item_geom(valid ? qb : 0, a.S, causal);
+            if (valid) {
+                // the first item's first key tile
+                ok = wait_k();
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t db = umma_desc_sw128(aV + vs * Cfg::K_TILE_BYTES + kk * 2048, Cfg::K_HALF, 1024);
-                    umma_f16_ts(tO, tS[s] + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                }
-                umma_commit(&pb->v_empty[vs]);
-                umma_commit(&pb->pv_done);
+                for (int t = 0; t < 2; ++t)
+                    if (ok && g.n[t] > 0) ok = issue_s(t, true, g.n[t] == 1);
+                if (ok) release_k();
             }
-            if (ok) umma_commit(&pb->o_full);
+            while (valid && ok) {
+                bool next_valid = false;
+                ItemGeom gn = g;
+                for (int j = 0; j < g.nmax && ok; ++j) {
+                    const bool last = (j == g.nmax - 1);
+                    if (last) {
+                        int nbh, nqbk;
+                        ok = sched_read(pb, a.status, taken, nbh, nqbk);
+                        if (!ok) break;
+                        sched_release(pb, taken++);
+                        next_valid = nbh >= 0;
+                        if (next_valid) gn = item_geom(nqbk, a.S, causal);
+                    }
+                    bool v_ready = false, k_ready = false;
+                    const uint32_t vs = vt % V_STAGES;
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (j < g.n[t]) {
+                            // ---- O_t (+)= P_t.V_j, in two halves of 64 keys as P_t arrives
+                            if (!v_ready) {
+                                ok = wait_bar(&pb->v_full[vs], (vt / V_STAGES) & 1u, pb, a.status);
+                                if (!ok) break;
+                                v_ready = true;
+                            }
+                            if (j == 0) { // the epilogue must have read the previous item's O_t
+                                ok = wait_bar(&pb->o_empty[t], (ci[t] & 1u) ^ 1u, pb, a.status);
+                                if (!ok) break;
+                            }
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                ok = wait_bar(&pb->p_full[t][half], cp[t] & 1u, pb, a.status);
+                                if (!ok) break;
+                                tc_fence_after();
+#pragma unroll
+                                for (int kk = half * 4; kk < half * 4 + 4; ++kk) {
+                                    const uint64_t db = umma_desc_sw128(aV + vs * TILE_BYTES + kk * 2048, HALF_BYTES, 1024);
+                                    umma_f16_ts(tO[t], tS[t] + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                                }
+                            }
+                            if (!ok) break;
+                            umma_commit(&pb->pv_done[t]);
+                            ++cp[t];
+                            if (j == g.n[t] - 1) {
+                                umma_commit(&pb->o_full[t]);
+                                ++ci[t];
+                            }
+                        }
+                        // ---- the next S of this query tile: key tile j+1, or the next item's first key tile
+                        bool use = false, first = false, last_s = false;
+                        if (j + 1 < g.n[t]) {
+                            use = true;
+                            last_s = (j + 2 == g.n[t]);
+                        } else if (last && next_valid && gn.n[t] > 0) {
+                            use = first = true;
+                            last_s = (gn.n[t] == 1);
+                        }
+                        if (use) {
+                            if (!k_ready) {
+                                ok = wait_k();
+                                if (!ok) break;
+                                k_ready = true;
+                            }
+                            ok = issue_s(t, first, last_s);
+                            if (!ok) break;
+                        }
+                    }
+                    if (!ok) break;
+                    if (v_ready) {
+                        umma_commit(&pb->v_empty[vs]);
+                        ++vt;
+                    }
+                    if (k_ready) release_k();
+                }
+                valid = next_valid;
+                g = gn;
+            }
         }
         __syncwarp();
-    } else {
-        // ======================= softmax / correction / epilogue (warps 2-5) =======================
+    } else if (warp < 12) {
+        // ======================= softmax: warps 4-7 query tile 0, warps 8-11 query tile 1 =======================
+        const int t = (warp - 4) >> 2;
         const int quarter = warp & 3;                  // TMEM lane quarter this warp may access
         const int lrow = quarter * 32 + lane;          // query row inside the tile
-        const int row = q0 + lrow;                     // query position
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const bool row_valid = row < a.S;
-        float m_used = -1e30f, l_sum = 0.f;
-        uint32_t r[NCH][32];
+        const uint32_t tS_t = tmem + (uint32_t)(t * BN), tO_t = tmem + 2u * BN + (uint32_t)(t * D);
+        uint64_t *const s_full = &pb->s_full[t], *const pv_done = &pb->pv_done[t], *const l_full = &pb->l_full[t],
+                        *const l_empty = &pb->l_empty[t], *const p_full = &pb->p_full[t][0];
+        uint32_t taken = 0, ct = 0, ci = 0;
         bool ok = true;
-
-        for (int j = 0; j < n_tiles; ++j) {
-            const int s = j & 1;
-            const uint32_t u = (uint32_t)(j >> 1);
-            const int k0 = j * BN;
-            if (warp == 2) TL(2, j, 0);
-            ok = wait_bar(&pb->s_full[s], u & 1u, pb, a.status);
+        for (;;) {
+            int bh, qb;
+            ok = sched_read(pb, a.status, taken, bh, qb);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (warp == 2) TL(2, j, 1);
-            if (j == 0) CT(1);
-            tc_fence_after();
-            // the whole score row of this tile into registers
-#pragma unroll
-            for (int ch = 0; ch < NCH; ++ch) tmem_ld32(tS[s] + lane_addr + ch * 32, r[ch]);
-            tmem_wait_ld();
-            if (warp == 2) TL(2, j, 2);
-
-            const bool check = (causal && k0 + BN - 1 > q0) || (k0 + BN > a.S) || (a.mask_mode == 1);
-            float m_tile = -INFINITY;
-            if (!check) {
-                // fast path: every key of the tile is visible; scale > 0 commutes with max
-#pragma unroll
-                for (int ch = 0; ch < NCH; ++ch)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(r[ch][i]));
-                m_tile *= a.scale_log2e;
-            } else {
-                // keys this row may see inside the tile: [0, lim); scores become scaled (+ mask) in place
+            __syncwarp();
+            if (lane == 0) sched_release(pb, taken);
+            ++taken;
+            if (bh < 0) break;
+            const ItemGeom g = item_geom(qb, a.S, causal);
+            const int n_t = t ? g.n[1] : g.n[0];
+            if (n_t == 0) continue;
+            const int q0 = t ? g.q0[1] : g.q0[0], row = q0 + lrow;
+            float m_used = -1e30f;
+            float2 l2 = make_float2(0.f, 0.f);
+            uint32_t ra[32], rb[32];
+            for (int j = 0; j < n_t; ++j) {
+                const int k0 = j * BN;
+                ok = wait_bar(s_full, ct & 1u, pb, a.status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t ts = tS_t + lane_addr;
+                const int mode = (a.mask_mode == 1) ? 2 : (((causal && k0 + BN - 1 > q0) || (k0 + BN > a.S)) ? 1 : 0);
+                // keys this row may see inside the tile: [0, lim)
                 int lim = min(BN, a.S - k0);
                 if (a.mask_mode == 2) lim = min(lim, row - k0 + 1);
                 if (a.mask_mode == 3) lim = min(lim, row - k0);
-                if (a.mask_mode != 1) {
-                    // causal diagonal / end of the prompt: an index test per key, no mask loads
-#pragma unroll
-                    for (int ch = 0; ch < NCH; ++ch)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const float x = (ch * 32 + i < lim) ? __uint_as_float(r[ch][i]) * a.scale_log2e : -INFINITY;
-                            r[ch][i] = __float_as_uint(x);
-                            m_tile = fmaxf(m_tile, x);
-                        }
-                } else {
-                    // the caller's additive mask, row = query position (rows beyond the prompt see nothing)
-                    const float *mrow = a.attn_mask + (size_t)min(row, a.S - 1) * a.mask_row_stride + k0;
-                    if (!row_valid) lim = 0;
-#pragma unroll
-                    for (int ch = 0; ch < NCH; ++ch)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int c = ch * 32 + i;
-                            float x = -INFINITY;
-                            if (c < lim) x = fmaf(__ldg(mrow + c), kLog2e, __uint_as_float(r[ch][i]) * a.scale_log2e);
-                            r[ch][i] = __float_as_uint(x);
-                            m_tile = fmaxf(m_tile, x);
-                        }
-                }
-            }
-            if (j == 0) {
-                m_used = fmaxf(m_tile, -1e30f);
-            } else {
-                const bool grow = m_tile > m_used + kRescaleThreshold;
-                if (__any_sync(0xffffffffu, grow)) {
-                    // O must hold every product up to tile j-1 before it is rescaled
-                    ok = wait_bar(&pb->pv_done, (uint32_t)((j - 1) & 1), pb, a.status);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const float m_new = fmaxf(m_used, m_tile);
-                    const float alpha = ex2(m_used - m_new);
-                    m_used = m_new;
-                    l_sum *= alpha;
-                    uint32_t o[32];
-#pragma unroll 1
-                    for (int ch = 0; ch < 4; ++ch) {
-                        tmem_ld32(tO + lane_addr + ch * 32, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(tO + lane_addr + ch * 32, o);
-                    }
-                }
-            }
-            // ---- P = exp2(x - m), row sum; fp16 pairs go back into the columns S_j came from
-            // (column c/2 of the buffer holds keys c, c+1), where the tensor core reads them as A
-            const float sc = check ? 1.0f : a.scale_log2e; // slow path scaled the scores already
-            const float neg_m = -m_used;
-#pragma unroll
-            for (int ch = 0; ch < NCH; ++ch) {
-                uint32_t packed[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2(fmaf(__uint_as_float(r[ch][i]), sc, neg_m));
-                    const float p1 = ex2(fmaf(__uint_as_float(r[ch][i + 1]), sc, neg_m));
-                    l_sum += p0 + p1;
-                    const __half2 h2 = __floats2half2_rn(p0, p1);
-                    packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&h2);
-                }
-                tmem_st16(tS[s] + lane_addr + ch * 16, packed);
-            }
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&pb->p_full[s]);
-            if (warp == 2) TL(2, j, 3);
-        }
-        if (warp == 2) TL(2, 63, 0);
-        CT(2);
+                if (mode == 2 && row >= a.S) lim = 0; // rows beyond the prompt: no mask row to read
+                const float *mrow = (mode == 2) ? a.attn_mask + (size_t)min(row, a.S - 1) * a.mask_row_stride + k0 : nullptr;
+                // ---- pass 1: the row maximum (the next 32 columns are in flight while 32 are reduced)
+                float m_tile = -INFINITY;
+                tmem_ld32(ts, ra);
+                tmem_wait_ld(ra);
+                tmem_ld32(ts + 32, rb);
+                if (mode == 0) m_tile = chunk_max<0>(ra, 0, lim, a.scale_log2e, mrow, m_tile);
+                else if (mode == 1) m_tile = chunk_max<1>(ra, 0, lim, a.scale_log2e, mrow, m_tile);
+                else m_tile = chunk_max<2>(ra, 0, lim, a.scale_log2e, mrow, m_tile);
+                tmem_wait_ld(rb);
+                tmem_ld32(ts + 64, ra);
+                if (mode == 0) m_tile = chunk_max<0>(rb, 32, lim, a.scale_log2e, mrow, m_tile);
+                else if (mode == 1) m_tile = chunk_max<1>(rb, 32, lim, a.scale_log2e, mrow, m_tile);
+                else m_tile = chunk_max<2>(rb, 32, lim, a.scale_log2e, mrow, m_tile);
+                tmem_wait_ld(ra);
+                tmem_ld32(ts + 96, rb);
+                if (mode == 0) m_tile = chunk_max<0>(ra, 64, lim, a.scale_log2e, mrow, m_tile);
+                else if (mode == 1) m_tile = chunk_max<1>(ra, 64, lim, a.scale_log2e, mrow, m_tile);
+                else m_tile = chunk_max<2>(ra, 64, lim, a.scale_log2e, mrow, m_tile);
+                tmem_wait_ld(rb);
+                tmem_ld32(ts, ra); // pass 2 starts over at column 0
+                if (mode == 0) m_tile = chunk_max<0>(rb, 96, lim, a.scale_log2e, mrow, m_tile) * a.scale_log2e; // scale > 0 commutes with max
+                else if (mode == 1) m_tile = chunk_max<1>(rb, 96, lim, a.scale_log2e, mrow, m_tile);
+                else m_tile = chunk_max<2>(rb, 96, lim, a.scale_log2e, mrow, m_tile);
 
-        // ---- epilogue: O / l
-        if (ok) {
-            ok = wait_bar(&pb->o_full, 0, pb, a.status);
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        CT(4);
-        if (ok) {
-            tc_fence_after();
-            const float inv = (l_sum > 0.f) ? 1.0f / l_sum : 0.f; // fully masked row -> zeros
-            // Every load has landed and every MMA has retired: the K/V rings are free.  Each warp
-            // stages its 32 rows there (padded rows: conflict-free 16-byte stores) and then writes
-            // them out with fully coalesced 16-byte stores, one or two whole rows per instruction.
-            const int esz = a.out_f16 ? 2 : 4;
-            const int rstride = D * esz + 16;
-            unsigned char *stg = sK + quarter * (32 * (D * 4 + 16));
-            uint32_t o[32];
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
-                tmem_ld32(tO + lane_addr + ch * 32, o);
-                tmem_wait_ld();
-                unsigned char *dst = stg + lane * rstride + ch * 32 * esz;
-                if (a.out_f16) {
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const __half2 h2 = __floats2half2_rn(__uint_as_float(o[8 * t + 2 * e]) * inv,
-                                                                 __uint_as_float(o[8 * t + 2 * e + 1]) * inv);
-                            w[e] = *reinterpret_cast<const uint32_t *>(&h2);
-                        }
-                        reinterpret_cast<uint4 *>(dst)[t] = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
+                if (j == 0) {
+                    m_used = fmaxf(m_tile, -1e30f);
                 } else {
+                    const bool grow = m_tile > m_used + kRescaleThreshold;
+                    if (__any_sync(0xffffffffu, grow)) {
+                        // O_t must hold every product up to tile j-1 before it is rescaled
+                        ok = wait_bar(pv_done, (ct - 1u) & 1u, pb, a.status);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const float m_new = fmaxf(m_used, m_tile);
+                        const float alpha = ex2(m_used - m_new);
+                        m_used = m_new;
+                        l2.x *= alpha;
+                        l2.y *= alpha;
+                        tmem_wait_ld(ra); // the pass-2 load issued above: one tcgen05.wait covers every load in flight
+                        uint32_t o[32];
+#pragma unroll 1
+                        for (int ch = 0; ch < 4; ++ch) {
+                            tmem_ld32(tO_t + lane_addr + ch * 32, o);
+                            tmem_wait_ld(o);
 #pragma unroll
-                    for (int t = 0; t < 8; ++t)
-                        reinterpret_cast<float4 *>(dst)[t] =
-                            make_float4(__uint_as_float(o[4 * t]) * inv, __uint_as_float(o[4 * t + 1]) * inv,
-                                        __uint_as_float(o[4 * t + 2]) * inv, __uint_as_float(o[4 * t + 3]) * inv);
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(tO_t + lane_addr + ch * 32, o);
+                        }
+                        tmem_wait_st();
+                    }
                 }
+                // ---- pass 2: P = exp2(x - m), row sum; each half of the row is handed to the tensor core as it is stored
+                const float neg_m = -m_used;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+                    uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+                    tmem_wait_ld(cur);
+                    if (c < 3) tmem_ld32(ts + (c + 1) * 32, nxt);
+                    uint32_t packed[16];
+                    if (mode == 0) chunk_exp<0, EMUL>(cur, c * 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                    else if (mode == 1) chunk_exp<1, EMUL>(cur, c * 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                    else chunk_exp<2, EMUL>(cur, c * 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                    tmem_st16(ts + c * 16, packed);
+                    if (c & 1) {
+                        tmem_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(p_full + (c >> 1));
+                    }
+                }
+                ++ct;
             }
+            if (!ok) break;
+            // ---- the item's row sums go to the epilogue warps through shared memory
+            if (ci > 0) {
+                ok = wait_bar(l_empty, (ci - 1u) & 1u, pb, a.status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
+            l_buf[t * BM + lrow] = l2.x + l2.y;
+            mbar_arrive(l_full);
+            ++ci;
+        }
+    } else {
+        // ======================= epilogue: warps 12-15, O_t / l -> global =======================
+        const int quarter = warp & 3;
+        const int lrow = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const int esz = a.out_f16 ? 2 : 4;
+        uint32_t taken = 0, ci[2] = {0, 0};
+        bool ok = true;
+        for (;;) {
+            int bh, qb;
+            ok = sched_read(pb, a.status, taken, bh, qb);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             __syncwarp();
-            const int lanes_per_row = D * esz / 16;      // 16 (fp16) or 32 (fp32)
-            const int rows_per_it = 32 / lanes_per_row;  // 2 or 1
-            const int rsub = lane / lanes_per_row, cchunk = lane % lanes_per_row;
-            unsigned char *gout = (unsigned char *)a.out + ((size_t)bh * a.S + q0 + quarter * 32) * D * esz;
-            for (int r0 = 0; r0 < 32; r0 += rows_per_it) {
-                const int rr = r0 + rsub;
-                if (q0 + quarter * 32 + rr < a.S)
-                    *reinterpret_cast<uint4 *>(gout + (size_t)rr * D * esz + cchunk * 16) =
-                        *reinterpret_cast<const uint4 *>(stg + rr * rstride + cchunk * 16);
+            if (lane == 0) sched_release(pb, taken);
+            ++taken;
+            if (bh < 0) break;
+            const ItemGeom g = item_geom(qb, a.S, causal);
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                if (g.n[t] == 0) continue;
+                ok = wait_bar(&pb->l_full[t], ci[t] & 1u, pb, a.status) && wait_bar(&pb->o_full[t], ci[t] & 1u, pb, a.status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const float l_sum = l_buf[t * BM + lrow];
+                mbar_arrive(&pb->l_empty[t]);
+                const float inv = (l_sum > 0.f) ? 1.0f / l_sum : 0.f; // fully masked row -> zeros
+                const int row = g.q0[t] + lrow;
+                unsigned char *gout = (unsigned char *)a.out + ((size_t)bh * a.S + row) * D * esz;
+                uint32_t o[32];
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    tmem_ld32(tO[t] + lane_addr + ch * 32, o);
+                    tmem_wait_ld(o);
+                    if (ch == 3) { // O_t is in registers: the next item may overwrite it
+                        tc_fence_before();
+                        mbar_arrive(&pb->o_empty[t]);
+                    }
+                    if (row < a.S) {
+                        if (a.out_f16) {
+                            uint4 *dst = reinterpret_cast<uint4 *>(gout + ch * 32 * 2);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const __half2 h2 = __floats2half2_rn(__uint_as_float(o[8 * q + 2 * e]) * inv,
+                                                                         __uint_as_float(o[8 * q + 2 * e + 1]) * inv);
+                                    w[e] = *reinterpret_cast<const uint32_t *>(&h2);
+                                }
+                                dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+                            float4 *dst = reinterpret_cast<float4 *>(gout + ch * 32 * 4);
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                dst[q] = make_float4(__uint_as_float(o[4 * q]) * inv, __uint_as_float(o[4 * q + 1]) * inv,
+                                                     __uint_as_float(o[4 * q + 2]) * inv, __uint_as_float(o[4 * q + 3]) * inv);
+                        }
+                    }
+                }
+                ++ci[t];
             }
+            if (!ok) break;
         }
     }
 
-    if (warp == 2) TL(2, 63, 1);
-    CT(3);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem, Cfg::TMEM_COLS);
+        tmem_dealloc(tmem, TMEM_COLS);
     }
 }
 
@@ -727,7 +957,6 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     a.status = reinterpret_cast<unsigned *>(sc);
 
     CUtensorMap tmQ, tmK, tmV;
-    constexpr int BN = kKeysPerTile;
     bool ok = make_map(enc, &tmQ, a.qh, B * H, S, S, BM);
     if (a.cache_f16) {
         ok = ok && make_map(enc, &tmK, p->k_cache, B * H, S, T, BN) && make_map(enc, &tmV, p->v_cache, B * H, S, T, BN);
@@ -735,19 +964,14 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
         ok = ok && make_map(enc, &tmK, a.kh, B * H, S, S, BN) && make_map(enc, &tmV, a.vh, B * H, S, S, BN);
     }
     if (!ok) return FLB_ERR_LAUNCH;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        return FLB_ERR_DEVICE;
 
-    // The attention kernel is launched with programmatic stream serialisation: its CTAs set themselves up
-    // (barriers, descriptors, TMEM) while the prologue drains and wait for it before they touch memory.  The
-    // prologue clears the status word itself, so no memset node sits between the two.
-    cudaLaunchAttribute pdl[1];
-    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    pdl[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.stream = stream;
-    cfg.attrs = pdl;
-    cfg.numAttrs = 1;
     const size_t pro_blocks = (size_t)B * H * ((S + 16 * kRowsPerThread - 1) / (16 * kRowsPerThread));
-    cfg.numAttrs = 0; // the prologue itself is launched the ordinary way (measured: starting it early costs 25 us)
+    cfg.numAttrs = 0; // the prologue is launched the ordinary way (measured: starting it early costs 25 us)
     cfg.gridDim = dim3((unsigned)pro_blocks);
     cfg.blockDim = dim3(256);
     cfg.dynamicSmemBytes = 0;
@@ -760,16 +984,22 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
         le = cudaLaunchKernelEx(&cfg, flb_prefill_prologue_kernel<2>, a);
     if (le != cudaSuccess) return FLB_ERR_LAUNCH;
 
-    static_assert(sizeof(PrefillBarriers) <= 256, "barrier block must fit its slot");
-    constexpr size_t smem = PrefillCfg<BN>::SMEM;
-    if (cudaFuncSetAttribute(flb_prefill_attn_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return FLB_ERR_LAUNCH;
-    const int nq = (S + BM - 1) / BM;
+    // The attention kernel is launched with programmatic stream serialisation: its CTAs set themselves up
+    // (barriers, descriptors, TMEM) while the prologue drains and wait for it before they touch memory.  The
+    // prologue clears the status words and the work counter itself, so no memset node sits between the two.
+    // One persistent CTA per SM; the CTAs pull their work items from the counter.
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    auto kern = flb_prefill_attn_kernel<kExpOnFmaEvery>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefillSmem) != cudaSuccess) return FLB_ERR_LAUNCH;
+    const long long num_items = (long long)B * H * ((S + 2 * BM - 1) / (2 * BM));
+    cfg.attrs = pdl;
     cfg.numAttrs = 1;
-    cfg.gridDim = dim3((unsigned)(B * H * nq));
+    cfg.gridDim = dim3((unsigned)(num_items < sms ? num_items : sms));
     cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    if (cudaLaunchKernelEx(&cfg, flb_prefill_attn_kernel<BN>, tmQ, tmK, tmV, a) != cudaSuccess) return FLB_ERR_LAUNCH;
+    cfg.dynamicSmemBytes = kPrefillSmem;
+    if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, a, (int)num_items) != cudaSuccess) return FLB_ERR_LAUNCH;
     if (p->out_q8) {
         flb_attn_quant_transpose_kernel<<<dim3((unsigned)S, (unsigned)B), 128, 0, stream>>>((const float *)p->out, p->out_q8,
                                                                                            p->out_q8_scale, H, S);
