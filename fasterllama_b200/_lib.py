@@ -73,6 +73,7 @@ class FlbAttnParams(C.Structure):
         ("out_head_total", C.c_int),
         ("out_head_offset", C.c_int),
         ("early_start", C.c_int),
+        ("qkv_row_stride", C.c_int),
     ]
 
 
@@ -111,6 +112,7 @@ EXPORTS = {
     "flb_attn_classify_mask": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_int), C.c_void_p]),
     "flb_attn_scratch_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint), C.c_void_p]),
     "flb_attn_decode_static_scratch": (C.c_int, [_PP, C.c_void_p]),
+    "flb_attn_static_scratch_status": (C.c_int, [C.POINTER(C.c_uint), C.c_void_p]),
     "flb_attn_peer_exchange": (C.c_int, [C.POINTER(FlbPeerExchange), C.c_void_p]),
     "flb_attn_quantize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
 }
@@ -141,7 +143,7 @@ def load_library(path: str | None = None) -> C.CDLL:
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.restype = res
         fn.argtypes = args
-    if lib.flb_attn_abi_version() != 3:
+    if lib.flb_attn_abi_version() != 4:
         raise RuntimeError("libflb_attn.so has an unexpected ABI version")
     if path is None:
         _lib = lib

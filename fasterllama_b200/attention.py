@@ -50,6 +50,21 @@ _IN_MODE = {"int32": FLB_IN_INT32, "float32": FLB_IN_F32, "float16": FLB_IN_F16}
 _DT = {"float32": FLB_F32, "float16": FLB_F16}
 
 
+def _token_row_stride(t: Any, B: int, S: int, H: int, d: int) -> int:
+    """Elements between the rows of two consecutive tokens of a q/k/v tensor shaped [B,S,H,d]: H*d when it is dense,
+    more when it is a column block of a wider [B*S, row] buffer (the output of one merged QKV projection).  Raises
+    for any other layout."""
+    if hasattr(t, "stride") and callable(t.stride):
+        st = tuple(int(x) for x in t.stride())
+    else:
+        st = tuple(int(x) // t.itemsize for x in t.strides)
+    row = st[1] if S > 1 else (st[0] if B > 1 else H * d)
+    ok = (d == 1 or st[3] == 1) and (H == 1 or st[2] == d) and (S == 1 or st[1] == row) and (B == 1 or st[0] == S * row) and row >= H * d
+    if not ok:
+        raise ValueError("q, k and v must be [B,S,H,d] with unit element stride, head stride d and one common token-row stride")
+    return row
+
+
 def make_params(
     *,
     q,
@@ -92,9 +107,13 @@ def make_params(
         raise ValueError("caches must be [B, H, T, d]")
     if out_peers is None and tuple(out.shape) != (B, H, S, d):
         raise ValueError("out must be [B, H, S, d]")
-    for name, t in (("q", q), ("k", k), ("v", v), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
+    for name, t in (("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
         if t is not None and not _is_contiguous(t):
             raise ValueError(f"{name} must be contiguous")
+    rows = {_token_row_stride(t, B, S, H, d) for t in (q, k, v)}
+    if len(rows) != 1:
+        raise ValueError("q, k and v must share one token-row stride")
+    row_stride = rows.pop()
     T = int(k_cache.shape[2])
     p = FlbAttnParams()
     p.batch_size, p.head_num, p.size_per_head, p.seq_len = B, H, d, S
@@ -103,6 +122,7 @@ def make_params(
     p.max_past_len = int(max_past_len)
     p.input_mode = _IN_MODE[_dtype_name(q)]
     p.q, p.k, p.v = _ptr(q), _ptr(k), _ptr(v)
+    p.qkv_row_stride = 0 if row_stride == H * d else row_stride
     p.act_scale, p.q_w_scale, p.k_w_scale, p.v_w_scale = _ptr(act_scale), _ptr(q_w_scale), _ptr(k_w_scale), _ptr(v_w_scale)
     p.freq_cis = _ptr(freq_cis)
     p.rope_pos0, p.rope_add_past = int(rope_pos0), int(bool(rope_add_past))
@@ -181,6 +201,13 @@ def decode_static_scratch(p: FlbAttnParams, stream=None) -> None:
     """Decode with the library's own fixed scratch block (for callers that cannot provide any):
     `p.scratch` is ignored.  One block per GPU — keep these calls on one stream."""
     _lib.check(_lib.load_library().flb_attn_decode_static_scratch(C.byref(p), _stream_handle(stream)))
+
+
+def static_scratch_status(stream=None) -> int:
+    """Error word of the calls made through `decode_static_scratch` on the current GPU (0 = clean)."""
+    st = C.c_uint(0)
+    _lib.check(_lib.load_library().flb_attn_static_scratch_status(C.byref(st), _stream_handle(stream)))
+    return int(st.value)
 
 
 def quantize(attn, q8, scale, stream=None) -> None:

@@ -64,11 +64,12 @@ template <> struct CacheIO<__half> {
     }
 };
 
-// One element of q/k/v for (unit = b*H + h, dim i) with seq_len == 1: [B,1,H,d] -> unit*d + i.
+// One element of q/k/v for sequence b, head h, dim i with seq_len == 1: [B,1,H,d] with row_stride elements
+// between sequences (H*d when dense).
 // FLB_IN_INT32: float(acc) * act_scale[b] * w_scale[h*d+i], in this order (decoder_kernels.cu:449).
 __device__ __forceinline__ float load_input(const DecodeArgs &a, const void *base, const float *w_scale, int unit, int b,
                                             int h, int i) {
-    const size_t off = (size_t)unit * kHeadDim + i;
+    const size_t off = (size_t)b * a.row_stride + (size_t)h * kHeadDim + i;
     if (a.input_mode == 0) {
         const float acc = (float)__ldg((const int32_t *)base + off);
         return acc * __ldg(a.act_scale + b) * __ldg(w_scale + (size_t)h * kHeadDim + i);

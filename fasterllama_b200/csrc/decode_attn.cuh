@@ -24,6 +24,7 @@ struct DecodeArgs {
     int split_len;
     int input_mode;
     const void *q, *k, *v;
+    int row_stride; // elements between two sequences' rows in q, k, v (H * d when they are dense)
     const float *act_scale, *q_w_scale, *k_w_scale, *v_w_scale;
     const float *freq_cis;
     int rope_pos0, rope_add_past;

@@ -68,6 +68,11 @@ int check_common(const flb_attn_params *p) {
         if (p->mask_row_stride <= 0) return FLB_ERR_BAD_SHAPE;
     }
     if (p->rope_pos0 < 0) return FLB_ERR_BAD_SHAPE;
+    if (p->qkv_row_stride != 0) {
+        if (p->qkv_row_stride < p->head_num * p->size_per_head) return FLB_ERR_BAD_SHAPE;
+        const int esz = (p->input_mode == FLB_IN_F16) ? 2 : 4;
+        if (((size_t)p->qkv_row_stride * esz) % 16u) return FLB_ERR_MISALIGNED;
+    }
     if (!aligned16(p->k_cache) || !aligned16(p->v_cache) || !aligned16(p->q) || !aligned16(p->k) ||
         !aligned16(p->v))
         return FLB_ERR_MISALIGNED;
@@ -178,6 +183,7 @@ int flb_attn_decode(const flb_attn_params *p, void *cuda_stream) {
     a.q = p->q;
     a.k = p->k;
     a.v = p->v;
+    a.row_stride = p->qkv_row_stride ? p->qkv_row_stride : p->head_num * flb::kHeadDim;
     a.act_scale = p->act_scale;
     a.q_w_scale = p->q_w_scale;
     a.k_w_scale = p->k_w_scale;

@@ -49,23 +49,22 @@ namespace {
 
 constexpr int D = 128;       // head dimension
 constexpr int BM = 128;      // query rows per tile (two tiles per work item)
-constexpr int BN = 128;      // keys per K/V tile
-constexpr int TILE_BYTES = 128 * D * 2;   // any 128-row fp16 tile (Q, K or V): 32 KB = two [128 x 64] swizzled blocks
+constexpr int BN = 64;       // keys per K/V tile
+constexpr int TILE_BYTES = BM * D * 2;    // query tile: 128 rows of fp16 = 32 KB, two [128 x 64] swizzled blocks
 constexpr int HALF_BYTES = TILE_BYTES / 2;
-#ifndef FLB_PF_K_STAGES
-#define FLB_PF_K_STAGES 3
-#endif
-#ifndef FLB_PF_V_STAGES
-#define FLB_PF_V_STAGES 2
+constexpr int KV_TILE_BYTES = BN * D * 2; // K or V tile: 64 keys = 16 KB, two [64 x 64] swizzled blocks
+constexpr int KV_HALF_BYTES = KV_TILE_BYTES / 2;
+constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES; // one ring stage: the K tile and the V tile of the same 64 keys
+#ifndef FLB_PF_KV_STAGES
+#define FLB_PF_KV_STAGES 5
 #endif
 #ifndef FLB_PF_EMUL
-#define FLB_PF_EMUL 4
+#define FLB_PF_EMUL 0
 #endif
-constexpr int K_STAGES = FLB_PF_K_STAGES; // K ring: a stage is free again once S = Q.K^T over it has completed
-constexpr int V_STAGES = FLB_PF_V_STAGES; // V ring: a stage is free again once O += P.V over it has completed
+constexpr int KV_STAGES = FLB_PF_KV_STAGES; // a stage is free again once both query tiles' O += P.V over it have completed
 constexpr int kExpOnFmaEvery = FLB_PF_EMUL; // every n-th exponential of a row on the FMA pipe (0 = none)
 constexpr int NUM_THREADS = 512;          // warps: 0 scheduler + K loads, 1 MMA, 2 V loads, 3 Q loads, 4-11 softmax, 12-15 epilogue
-constexpr uint32_t TMEM_COLS = 512;       // S0, S1, O0, O1: 128 columns each
+constexpr uint32_t TMEM_COLS = 512;       // per query tile: two score buffers of 64 columns + 128 columns of O
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f; // log2 domain: P stays below 2^8, exact in fp16 range
 constexpr int kWorkCounterWord = 4;       // word of the status header the work scheduler counts in (cleared by the prologue)
@@ -76,6 +75,7 @@ struct PrefillArgs {
     int B, H, S, T;
     int input_mode;
     const void *q, *k, *v;
+    int row_stride; // elements between two tokens' rows in q, k, v (H * d when they are dense)
     const float *act_scale, *q_w_scale, *k_w_scale, *v_w_scale;
     const float *freq_cis;
     int rope_pos0;
@@ -191,7 +191,7 @@ template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int s = min(s0 + 16 * r, a.S - 1); // rows past the end load a valid row and are not stored
-        const size_t in_off = (((size_t)b * a.S + s) * a.H + h) * D + c * 8;
+        const size_t in_off = ((size_t)b * a.S + s) * a.row_stride + (size_t)h * D + c * 8;
         rq[r] = load_raw8<MODE>(a.q, in_off);
         rk[r] = load_raw8<MODE>(a.k, in_off);
         rv[r] = load_raw8<MODE>(a.v, in_off);
@@ -244,25 +244,32 @@ template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_
 // attention
 // ------------------------------------------------------------------------------------------------
 constexpr int SCHED_DEPTH = 4;        // work items the scheduler may publish ahead
-constexpr int kSchedConsumers = 15;   // V loader, Q loader, MMA issuer, 8 softmax warps, 4 epilogue warps
+constexpr int kSchedConsumers = 15;   // two S issuers, the P.V issuer, 8 softmax warps, 4 epilogue warps
 constexpr int kHeadsPerGroup = 32;    // work list: groups of this many (b,h) units, heavy query blocks first inside a group
 
 struct __align__(8) PrefillBarriers {
     uint64_t q_full[2], q_empty[2];   // per query tile of the item
-    uint64_t k_full[K_STAGES], k_empty[K_STAGES];
-    uint64_t v_full[V_STAGES], v_empty[V_STAGES];
-    uint64_t s_full[2];               // S_t = Q_t.K_j^T landed in TMEM
-    uint64_t p_full[2][2];            // P_t written over S_t's columns: keys 0..63, keys 64..127 (128 arrivals each)
-    uint64_t pv_done[2];              // O_t += P_t.V_j retired (one phase per tile)
+    uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES]; // K and V tile of 64 keys landed / both query tiles are done with them
+    uint64_t s_full[2][2];            // [t][buffer] S = Q_t.K_j^T landed in score buffer j & 1 of query tile t
+    uint64_t p_full[2][2];            // [t][buffer] P_j written over the scores by the 128 softmax threads of query tile t
+    uint64_t pv_done[2][2];           // [t][buffer] O_t += P_j.V_j retired: score buffer j & 1 may take S_{j+2}
     uint64_t o_full[2], o_empty[2];   // last P.V of an item retired / the epilogue has read O_t out of TMEM
     uint64_t l_full[2], l_empty[2];   // row sums of an item in shared memory / read by the epilogue
     uint64_t sched_full[SCHED_DEPTH], sched_empty[SCHED_DEPTH];
     int sched_bh[SCHED_DEPTH], sched_qb[SCHED_DEPTH]; // the published items; bh < 0 = no more work
     uint32_t tmem_base;
     int abort_flag;
+#ifdef FLB_PF_TRACE
+    uint32_t tr_clk[176];
+    unsigned short tr_code[176];
+#endif
 };
+#ifdef FLB_PF_TRACE
+constexpr int kBarrierSlot = 512 + 1056;
+#else
 constexpr int kBarrierSlot = 512;
-constexpr size_t kPrefillSmem = (size_t)(2 + K_STAGES + V_STAGES) * TILE_BYTES + 2 * BM * sizeof(float) + kBarrierSlot;
+#endif
+constexpr size_t kPrefillSmem = 2 * (size_t)TILE_BYTES + (size_t)KV_STAGES * STAGE_BYTES + 2 * BM * sizeof(float) + kBarrierSlot;
 static_assert(sizeof(PrefillBarriers) <= kBarrierSlot, "barrier block must fit its slot");
 static_assert(kPrefillSmem <= 232448, "exceeds the 227 KB a CTA may use");
 
@@ -272,9 +279,10 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
-// Bounded wait (0.2 s of wall clock).  On failure raises the CTA's abort flag and the status bit.
-__device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, PrefillBarriers *pb, unsigned *status) {
-    if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait (0.2 s of wall clock).  On failure raises the CTA's abort flag and the status bit.  The slow part is
+// kept out of line: the common case (the phase has completed, or completes within one try_wait, which itself
+// suspends the thread for a while) is two instructions at the call site.
+__device__ __noinline__ bool wait_bar_slow(uint64_t *bar, uint32_t parity, PrefillBarriers *pb, unsigned *status) {
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -287,11 +295,24 @@ __device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, Prefill
     atomicOr(status, kErrPrefillWait);
     return false;
 }
+__device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, PrefillBarriers *pb, unsigned *status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return wait_bar_slow(bar, parity, pb, status);
+}
+
+#ifdef FLB_PF_TRACE
+// TEMPORARY tuning aid: SM clock stamps of CTA 0's MMA-issuing thread, kept in shared memory (cheap) and dumped
+// into the (unused with an fp16 cache) K staging area when the kernel ends.
+#define TRACE_MAX 176
+#define TR(code) do { if (blockIdx.x == 0 && (code) < 0x200 && tr_on && tr_n < TRACE_MAX) { uint32_t c_; asm volatile("mov.u32 %0, %%clock;" : "=r"(c_)); pb->tr_clk[tr_n] = c_; pb->tr_code[tr_n] = (unsigned short)(code); ++tr_n; } } while (0)
+#else
+#define TR(code) do { } while (0)
+#endif
 
 // A work item is 256 query rows of one (b,h): two 128-row tiles, each with its own S/P and O columns in TMEM.
 struct ItemGeom {
     int q0[2];   // first query row of tile t
-    int n[2];    // key tiles tile t attends over (0 = the tile lies beyond the prompt)
+    int n[2];    // key tiles query tile t attends over (n[0] <= n[1])
     int nmax;
 };
 __device__ __forceinline__ ItemGeom item_geom(int qb, int S, bool causal) {
@@ -300,8 +321,10 @@ __device__ __forceinline__ ItemGeom item_geom(int qb, int S, bool causal) {
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
         g.q0[t] = qb * (2 * BM) + t * BM;
-        // causal modes skip the key tiles above the diagonal: tile t ends at key q0 + 127
-        g.n[t] = (g.q0[t] < S) ? (causal ? min(n_all, g.q0[t] / BN + 1) : n_all) : 0;
+        // causal modes skip the key tiles above the diagonal: query tile t ends at row q0 + 127.  A query tile that
+        // lies beyond the prompt (the second tile of a ragged last block) is worked on like any other: its rows are
+        // zero-filled by the loads and never stored, and every role keeps the same step pattern for every item.
+        g.n[t] = causal ? min(n_all, (g.q0[t] + BM - 1) / BN + 1) : n_all;
     }
     g.nmax = max(g.n[0], g.n[1]);
     return g;
@@ -363,9 +386,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     // The 128-byte swizzle pattern is a function of address bits [4,10): tiles must start on 1 KB.
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char *sQ = smem;                                  // two query tiles
-    unsigned char *sK = sQ + 2 * TILE_BYTES;                   // K ring
-    unsigned char *sV = sK + K_STAGES * TILE_BYTES;            // V ring
-    float *l_buf = reinterpret_cast<float *>(sV + V_STAGES * TILE_BYTES); // [2][128] row sums of the item being finished
+    unsigned char *sKV = sQ + 2 * TILE_BYTES;                  // K/V ring: stage = K tile, then V tile
+    float *l_buf = reinterpret_cast<float *>(sKV + KV_STAGES * STAGE_BYTES); // [2][128] row sums of the item being finished
     PrefillBarriers *pb = reinterpret_cast<PrefillBarriers *>(l_buf + 2 * BM);
     if (smem_u32(smem) & 1023u) { // never observed; without it the MMAs would read scrambled tiles
         grid_dependency_wait();
@@ -381,22 +403,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         for (int t = 0; t < 2; ++t) {
             mbar_init(&pb->q_full[t], 1);
             mbar_init(&pb->q_empty[t], 1);
-            mbar_init(&pb->s_full[t], 1);
+            mbar_init(&pb->s_full[t][0], 1);
+            mbar_init(&pb->s_full[t][1], 1);
             mbar_init(&pb->p_full[t][0], BM);
             mbar_init(&pb->p_full[t][1], BM);
-            mbar_init(&pb->pv_done[t], 1);
+            mbar_init(&pb->pv_done[t][0], 1);
+            mbar_init(&pb->pv_done[t][1], 1);
             mbar_init(&pb->o_full[t], 1);
             mbar_init(&pb->o_empty[t], BM);
             mbar_init(&pb->l_full[t], BM);
             mbar_init(&pb->l_empty[t], BM);
         }
-        for (int s = 0; s < K_STAGES; ++s) {
-            mbar_init(&pb->k_full[s], 1);
-            mbar_init(&pb->k_empty[s], 1);
-        }
-        for (int s = 0; s < V_STAGES; ++s) {
-            mbar_init(&pb->v_full[s], 1);
-            mbar_init(&pb->v_empty[s], 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(&pb->kv_full[s], 1);
+            mbar_init(&pb->kv_empty[s], 1); // the P.V issuer: both query tiles' products over it have retired
         }
         for (int s = 0; s < SCHED_DEPTH; ++s) {
             mbar_init(&pb->sched_full[s], 1);
@@ -422,11 +442,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     grid_dependency_wait();
     grid_launch_dependents();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&pb->tmem_base);
-    const uint32_t tS[2] = {tmem, tmem + (uint32_t)BN};
-    const uint32_t tO[2] = {tmem + 2u * BN, tmem + 2u * BN + (uint32_t)D};
+    // TMEM columns: query tile t has its two score buffers at 128 t and 128 t + 64, its accumulator O_t at 256 + 128 t
+    const uint32_t tO[2] = {tmem + 256u, tmem + 256u + (uint32_t)D};
 
     if (warp == 0) {
-        // ======================= work scheduler + K loader =======================
+        // ======================= work scheduler + K/V loader =======================
         if (lane == 0) {
             unsigned *counter = a.status + kWorkCounterWord;
             const int BH = a.B * a.H;
@@ -466,11 +486,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 return k < (unsigned)num_items ? (int)k : -1;
             };
             auto load_k = [&](int bh, int j) -> bool {
-                const uint32_t s = kt % K_STAGES;
-                if (!wait_bar(&pb->k_empty[s], ((kt / K_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
-                mbar_arrive_expect_tx(&pb->k_full[s], TILE_BYTES);
-                tma_load_3d(sK + s * TILE_BYTES, &tmK, 0, j * BN, bh, &pb->k_full[s]);
-                tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, 64, j * BN, bh, &pb->k_full[s]);
+                const uint32_t s = kt % KV_STAGES;
+                if (!wait_bar(&pb->kv_empty[s], ((kt / KV_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
+                unsigned char *dst = sKV + s * STAGE_BYTES;
+                mbar_arrive_expect_tx(&pb->kv_full[s], STAGE_BYTES);
+                tma_load_3d(dst, &tmK, 0, j * BN, bh, &pb->kv_full[s]);
+                tma_load_3d(dst + KV_HALF_BYTES, &tmK, 64, j * BN, bh, &pb->kv_full[s]);
+                tma_load_3d(dst + KV_TILE_BYTES, &tmV, 0, j * BN, bh, &pb->kv_full[s]);
+                tma_load_3d(dst + KV_TILE_BYTES + KV_HALF_BYTES, &tmV, 64, j * BN, bh, &pb->kv_full[s]);
                 ++kt;
                 return true;
             };
@@ -488,182 +511,152 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
         }
         __syncwarp();
-    } else if (warp == 2) {
-        // ======================= V loader =======================
+    } else if (warp == 1 || warp == 3) {
+        // ======================= S issuers: warp 1 for query tile 0, warp 3 for query tile 1 =======================
+        // tcgen05.mma is issued by single threads, and one thread cannot issue (and wait, and commit) fast enough for the
+        // pipe: three do it.  These two issue S = Q_t.K_j^T, each for its query tile, and load that tile's query rows;
+        // warp 2 issues every P.V.  A query tile has two score buffers, and its S runs two key tiles ahead of its P.V:
+        // while the softmax threads work on S_j, S_{j+1} is already in TMEM and P_{j-1}.V_{j-1} is running, so the
+        // softmax warps never wait for the tensor pipe.  S_{j+2} overwrites score buffer j & 1, which P_j occupied: it is
+        // issued once P_j.V_j has retired (pv_done).  The stream of key tiles runs across work items.  Every descriptor is
+        // a constant plus a start address computed once: the loop is a few dozen instructions.
         if (lane == 0) {
-            uint32_t taken = 0, vt = 0;
-            for (;;) {
-                int bh, qb;
-                if (!sched_read(pb, a.status, taken, bh, qb)) break;
-                sched_release(pb, taken++);
-                if (bh < 0) break;
-                const ItemGeom g = item_geom(qb, a.S, causal);
-                bool ok = true;
-                for (int j = 0; j < g.nmax && ok; ++j) {
-                    const uint32_t s = vt % V_STAGES;
-                    ok = wait_bar(&pb->v_empty[s], ((vt / V_STAGES) & 1u) ^ 1u, pb, a.status);
+            const int t = warp >> 1;
+            // A (Q) and B (K) both K-major, 128-byte swizzle, 8-row groups 1024 B apart
+            constexpr uint32_t idesc_qk = umma_idesc_f16(BM, BN, false, false);
+            const uint32_t tS_t = tmem + (uint32_t)(t * 128);
+            // descriptor start addresses count 16-byte units
+            const uint64_t dq0 = umma_desc_sw128(smem_u32(sQ) + t * TILE_BYTES, 16, 1024);
+            const uint64_t dk0 = umma_desc_sw128(smem_u32(sKV), 16, 1024);
+            uint64_t *const q_full = &pb->q_full[t], *const q_empty = &pb->q_empty[t], *const s_full = &pb->s_full[t][0],
+                            *const pv_done = &pb->pv_done[t][0];
+            unsigned char *const sQ_t = sQ + t * TILE_BYTES;
+            uint32_t taken = 0, kt = 0, gs = 0, nq = 0; // items read, ring tiles passed, S issued, query tiles loaded
+            int nmax = 0, n_t = 0, j = 0;
+            bool ok = true, valid = true;
+#ifdef FLB_PF_TRACE
+            uint32_t tr_n = 0, tr_iter = 0;
+            bool tr_on = false;
+#endif
+            while (ok && valid) {
+                if (j == nmax) {
+                    // ---- next work item: its query rows go into the tile's buffer as soon as the previous item's
+                    // last S has retired.  The two key tiles of lead hide the load's latency from the softmax warps.
+                    int bh, qb;
+                    ok = sched_read(pb, a.status, taken, bh, qb);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(&pb->v_full[s], TILE_BYTES);
-                    tma_load_3d(sV + s * TILE_BYTES, &tmV, 0, j * BN, bh, &pb->v_full[s]);
-                    tma_load_3d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, 64, j * BN, bh, &pb->v_full[s]);
-                    ++vt;
+                    sched_release(pb, taken++);
+                    valid = bh >= 0;
+                    if (!valid) break;
+                    const ItemGeom g = item_geom(qb, a.S, causal);
+                    nmax = g.nmax;
+                    n_t = t ? g.n[1] : g.n[0];
+                    j = 0;
+                    if (nq > 0) {
+                        ok = wait_bar(q_empty, (nq - 1u) & 1u, pb, a.status);
+                        if (!ok) break;
+                    }
+                    mbar_arrive_expect_tx(q_full, TILE_BYTES);
+                    tma_load_3d(sQ_t, &tmQ, 0, t ? g.q0[1] : g.q0[0], bh, q_full);
+                    tma_load_3d(sQ_t + HALF_BYTES, &tmQ, 64, t ? g.q0[1] : g.q0[0], bh, q_full);
+                    ++nq;
+                    continue;
                 }
+                const uint32_t ks = kt % KV_STAGES;
+                ok = wait_bar(&pb->kv_full[ks], (kt / KV_STAGES) & 1u, pb, a.status);
                 if (!ok) break;
+                ++kt;
+                if (j >= n_t) { // above this query tile's diagonal
+                    ++j;
+                    continue;
+                }
+#ifdef FLB_PF_TRACE
+                tr_on = (t == 0) && (++tr_iter >= FLB_PF_TRACE);
+                TR(0x1f0);
+#endif
+                if (j == 0) ok = wait_bar(q_full, (nq - 1u) & 1u, pb, a.status);
+                const uint32_t buf = gs & 1u;
+                if (ok && gs >= 2) ok = wait_bar(pv_done + buf, ((gs - 2u) >> 1) & 1u, pb, a.status); // P_{j-2}.V_{j-2} has read this buffer
+                if (!ok) break;
+                TR(0x107);
+                tc_fence_after();
+                const uint64_t dk = dk0 + (uint64_t)(ks * (uint32_t)(STAGE_BYTES >> 4));
+                const uint32_t ts = tS_t + buf * (uint32_t)BN;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) { // dims 16 kk .. 16 kk + 15
+                    const uint32_t oq = (uint32_t)((kk >> 2) * (HALF_BYTES >> 4) + (kk & 3) * 2);
+                    const uint32_t okk = (uint32_t)((kk >> 2) * (KV_HALF_BYTES >> 4) + (kk & 3) * 2);
+                    umma_f16_ss(ts, dq0 + oq, dk + okk, idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full + buf);
+                if (j == n_t - 1) umma_commit(q_empty); // the query tile's buffer may take the next item's rows
+                TR(0x108);
+                ++gs;
+                ++j;
             }
+#ifdef FLB_PF_TRACE
+            if (blockIdx.x == 0 && t == 0) {
+                uint64_t *dst = reinterpret_cast<uint64_t *>(a.kh);
+                dst[0] = tr_n;
+                for (uint32_t i = 0; i < tr_n; ++i) dst[1 + i] = ((uint64_t)pb->tr_code[i] << 32) | pb->tr_clk[i];
+            }
+#endif
         }
         __syncwarp();
-    } else if (warp == 3) {
-        // ======================= Q loader =======================
+    } else if (warp == 2) {
+        // ======================= P.V issuer (both query tiles) =======================
+        // O_t (+)= P_j.V_j for t = 0, 1 over every ring tile: P read from TMEM as the A operand (fp16 pairs in the
+        // columns S came from), V from shared memory as an MN-major B operand (the two 64-dim blocks KV_HALF_BYTES
+        // apart (LBO), 8-key groups 1024 B apart (SBO)).  The stage goes back to the loader when both have retired.
         if (lane == 0) {
-            uint32_t taken = 0, cq[2] = {0, 0};
+            constexpr uint32_t idesc_pv = umma_idesc_f16(BM, D, false, true);
+            const uint64_t dv0 = umma_desc_sw128(smem_u32(sKV) + KV_TILE_BYTES, KV_HALF_BYTES, 1024);
+            uint32_t taken = 0, vt = 0, gp[2] = {0, 0}, ci[2] = {0, 0};
+            int nmax = 0, n[2] = {0, 0}, j = 0;
+            bool ok = true;
             for (;;) {
-                int bh, qb;
-                if (!sched_read(pb, a.status, taken, bh, qb)) break;
-                sched_release(pb, taken++);
-                if (bh < 0) break;
-                const ItemGeom g = item_geom(qb, a.S, causal);
-                bool ok = true;
+                if (j == nmax) {
+                    int bh, qb;
+                    ok = sched_read(pb, a.status, taken, bh, qb);
+                    if (!ok) break;
+                    sched_release(pb, taken++);
+                    if (bh < 0) break;
+                    const ItemGeom g = item_geom(qb, a.S, causal);
+                    nmax = g.nmax;
+                    n[0] = g.n[0];
+                    n[1] = g.n[1];
+                    j = 0;
+                    continue;
+                }
+                // No wait for the stage: a P exists only after its S, whose issuer has waited for the stage to land.
+                const uint32_t vs = vt % KV_STAGES;
+                const uint64_t dv = dv0 + (uint64_t)(vs * (uint32_t)(STAGE_BYTES >> 4));
+                ++vt;
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
-                    if (g.n[t] == 0 || !ok) continue;
-                    // free again once the last S of the previous item on this tile has been computed
-                    ok = wait_bar(&pb->q_empty[t], (cq[t] & 1u) ^ 1u, pb, a.status);
-                    if (!ok) break;
-                    mbar_arrive_expect_tx(&pb->q_full[t], TILE_BYTES);
-                    tma_load_3d(sQ + t * TILE_BYTES, &tmQ, 0, g.q0[t], bh, &pb->q_full[t]);
-                    tma_load_3d(sQ + t * TILE_BYTES + HALF_BYTES, &tmQ, 64, g.q0[t], bh, &pb->q_full[t]);
-                    ++cq[t];
+                    if (j >= n[t] || !ok) continue; // above this query tile's diagonal
+                    if (j == 0) { // the epilogue has read the previous item's O_t
+                        ok = wait_bar(&pb->o_empty[t], (ci[t] & 1u) ^ 1u, pb, a.status);
+                        if (!ok) continue;
+                    }
+                    const uint32_t buf = gp[t] & 1u;
+                    ok = wait_bar(&pb->p_full[t][buf], (gp[t] >> 1) & 1u, pb, a.status);
+                    if (!ok) continue;
+                    tc_fence_after();
+                    const uint32_t tp = tmem + (uint32_t)(t * 128) + buf * (uint32_t)BN;
+#pragma unroll
+                    for (int kk = 0; kk < BN / 16; ++kk) // 16 keys = 2048 bytes of the tile per step
+                        umma_f16_ts(tO[t], tp + kk * 8, dv + (uint32_t)(kk * (2048 >> 4)), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(&pb->pv_done[t][buf]);
+                    if (j == n[t] - 1) {
+                        umma_commit(&pb->o_full[t]);
+                        ++ci[t];
+                    }
+                    ++gp[t];
                 }
                 if (!ok) break;
-            }
-        }
-        __syncwarp();
-    } else if (warp == 1) {
-        // ======================= MMA issuer =======================
-        if (lane == 0) {
-            // S = Q.K^T : A (Q) and B (K) both K-major, 128-byte swizzle, 8-row groups 1024 B apart
-            constexpr uint32_t idesc_qk = umma_idesc_f16(BM, BN, false, false);
-            // O += P.V  : A (P) from TMEM (fp16 pairs in the columns S came from); B (V) MN-major: the two 64-dim
-            // blocks HALF_BYTES apart (LBO), 8-key groups 1024 B apart (SBO)
-            constexpr uint32_t idesc_pv = umma_idesc_f16(BM, D, false, true);
-            const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
-            uint32_t taken = 0, kt = 0, vt = 0;
-            uint32_t cq[2] = {0, 0}, cp[2] = {0, 0}, ci[2] = {0, 0};
-            bool ok = true;
-
-            // The tensor pipe executes this thread's MMAs in issue order: ... PV0_j, S0_{j+1}, PV1_j, S1_{j+1}, ...
-            // so S_t overwrites its TMEM buffer only after the P.V that read P_t from it.
-            auto issue_s = [&](int t, bool first_of_item, bool last_of_item) -> bool {
-                if (first_of_item) {
-                    if (!wait_bar(&pb->q_full[t], cq[t] & 1u, pb, a.status)) return false;
-                    ++cq[t];
-                }
-                tc_fence_after();
-                const uint32_t ks = kt % K_STAGES;
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint64_t da = umma_desc_sw128(aQ + t * TILE_BYTES + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
-                    const uint64_t db = umma_desc_sw128(aK + ks * TILE_BYTES + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
-                    umma_f16_ss(tS[t], da, db, idesc_qk, kk > 0 ? 1u : 0u);
-                }
-                umma_commit(&pb->s_full[t]);
-                if (last_of_item) umma_commit(&pb->q_empty[t]);
-                return true;
-            };
-            auto wait_k = [&]() -> bool { return wait_bar(&pb->k_full[kt % K_STAGES], (kt / K_STAGES) & 1u, pb, a.status); };
-            auto release_k = [&]() {
-                umma_commit(&pb->k_empty[kt % K_STAGES]);
-                ++kt;
-            };
-
-            int bh, qb;
-            ok = sched_read(pb, a.status, taken, bh, qb);
-            if (ok) sched_release(pb, taken++);
-            bool valid = ok && bh >= 0;
-            ItemGeom g = item_geom(valid ? qb : 0, a.S, causal);
-            if (valid) {
-                // the first item's first key tile
-                ok = wait_k();
-#pragma unroll
-                for (int t = 0; t < 2; ++t)
-                    if (ok && g.n[t] > 0) ok = issue_s(t, true, g.n[t] == 1);
-                if (ok) release_k();
-            }
-            while (valid && ok) {
-                bool next_valid = false;
-                ItemGeom gn = g;
-                for (int j = 0; j < g.nmax && ok; ++j) {
-                    const bool last = (j == g.nmax - 1);
-                    if (last) {
-                        int nbh, nqbk;
-                        ok = sched_read(pb, a.status, taken, nbh, nqbk);
-                        if (!ok) break;
-                        sched_release(pb, taken++);
-                        next_valid = nbh >= 0;
-                        if (next_valid) gn = item_geom(nqbk, a.S, causal);
-                    }
-                    bool v_ready = false, k_ready = false;
-                    const uint32_t vs = vt % V_STAGES;
-#pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        if (j < g.n[t]) {
-                            // ---- O_t (+)= P_t.V_j, in two halves of 64 keys as P_t arrives
-                            if (!v_ready) {
-                                ok = wait_bar(&pb->v_full[vs], (vt / V_STAGES) & 1u, pb, a.status);
-                                if (!ok) break;
-                                v_ready = true;
-                            }
-                            if (j == 0) { // the epilogue must have read the previous item's O_t
-                                ok = wait_bar(&pb->o_empty[t], (ci[t] & 1u) ^ 1u, pb, a.status);
-                                if (!ok) break;
-                            }
-#pragma unroll
-                            for (int half = 0; half < 2; ++half) {
-                                ok = wait_bar(&pb->p_full[t][half], cp[t] & 1u, pb, a.status);
-                                if (!ok) break;
-                                tc_fence_after();
-#pragma unroll
-                                for (int kk = half * 4; kk < half * 4 + 4; ++kk) {
-                                    const uint64_t db = umma_desc_sw128(aV + vs * TILE_BYTES + kk * 2048, HALF_BYTES, 1024);
-                                    umma_f16_ts(tO[t], tS[t] + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                                }
-                            }
-                            if (!ok) break;
-                            umma_commit(&pb->pv_done[t]);
-                            ++cp[t];
-                            if (j == g.n[t] - 1) {
-                                umma_commit(&pb->o_full[t]);
-                                ++ci[t];
-                            }
-                        }
-                        // ---- the next S of this query tile: key tile j+1, or the next item's first key tile
-                        bool use = false, first = false, last_s = false;
-                        if (j + 1 < g.n[t]) {
-                            use = true;
-                            last_s = (j + 2 == g.n[t]);
-                        } else if (last && next_valid && gn.n[t] > 0) {
-                            use = first = true;
-                            last_s = (gn.n[t] == 1);
-                        }
-                        if (use) {
-                            if (!k_ready) {
-                                ok = wait_k();
-                                if (!ok) break;
-                                k_ready = true;
-                            }
-                            ok = issue_s(t, first, last_s);
-                            if (!ok) break;
-                        }
-                    }
-                    if (!ok) break;
-                    if (v_ready) {
-                        umma_commit(&pb->v_empty[vs]);
-                        ++vt;
-                    }
-                    if (k_ready) release_k();
-                }
-                valid = next_valid;
-                g = gn;
+                umma_commit(&pb->kv_empty[vs]);
+                ++j;
             }
         }
         __syncwarp();
@@ -673,8 +666,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int quarter = warp & 3;                  // TMEM lane quarter this warp may access
         const int lrow = quarter * 32 + lane;          // query row inside the tile
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const uint32_t tS_t = tmem + (uint32_t)(t * BN), tO_t = tmem + 2u * BN + (uint32_t)(t * D);
-        uint64_t *const s_full = &pb->s_full[t], *const pv_done = &pb->pv_done[t], *const l_full = &pb->l_full[t],
+        const uint32_t tS_t = tmem + (uint32_t)(t * 128), tO_t = tmem + 256u + (uint32_t)(t * D);
+        uint64_t *const s_full = &pb->s_full[t][0], *const pv_done = &pb->pv_done[t][0], *const l_full = &pb->l_full[t],
                         *const l_empty = &pb->l_empty[t], *const p_full = &pb->p_full[t][0];
         uint32_t taken = 0, ct = 0, ci = 0;
         bool ok = true;
@@ -695,12 +688,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             float2 l2 = make_float2(0.f, 0.f);
             uint32_t ra[32], rb[32];
             for (int j = 0; j < n_t; ++j) {
+                // One key tile = one step of the online softmax: load the 64 scores of this row, maximum, (rarely)
+                // rescale, P = 2^(x - m) stored over the scores as fp16 pairs, hand the buffer to the tensor core.
                 const int k0 = j * BN;
-                ok = wait_bar(s_full, ct & 1u, pb, a.status);
+                const uint32_t buf = ct & 1u;
+                ok = wait_bar(s_full + buf, (ct >> 1) & 1u, pb, a.status);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t ts = tS_t + lane_addr;
+                const uint32_t ts = tS_t + buf * (uint32_t)BN + lane_addr;
+                tmem_ld32(ts, ra);
+                tmem_ld32(ts + 32, rb);
                 const int mode = (a.mask_mode == 1) ? 2 : (((causal && k0 + BN - 1 > q0) || (k0 + BN > a.S)) ? 1 : 0);
                 // keys this row may see inside the tile: [0, lim)
                 int lim = min(BN, a.S - k0);
@@ -708,37 +706,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (a.mask_mode == 3) lim = min(lim, row - k0);
                 if (mode == 2 && row >= a.S) lim = 0; // rows beyond the prompt: no mask row to read
                 const float *mrow = (mode == 2) ? a.attn_mask + (size_t)min(row, a.S - 1) * a.mask_row_stride + k0 : nullptr;
-                // ---- pass 1: the row maximum (the next 32 columns are in flight while 32 are reduced)
+                tmem_wait_ld(ra, rb);
                 float m_tile = -INFINITY;
-                tmem_ld32(ts, ra);
-                tmem_wait_ld(ra);
-                tmem_ld32(ts + 32, rb);
-                if (mode == 0) m_tile = chunk_max<0>(ra, 0, lim, a.scale_log2e, mrow, m_tile);
-                else if (mode == 1) m_tile = chunk_max<1>(ra, 0, lim, a.scale_log2e, mrow, m_tile);
-                else m_tile = chunk_max<2>(ra, 0, lim, a.scale_log2e, mrow, m_tile);
-                tmem_wait_ld(rb);
-                tmem_ld32(ts + 64, ra);
-                if (mode == 0) m_tile = chunk_max<0>(rb, 32, lim, a.scale_log2e, mrow, m_tile);
-                else if (mode == 1) m_tile = chunk_max<1>(rb, 32, lim, a.scale_log2e, mrow, m_tile);
-                else m_tile = chunk_max<2>(rb, 32, lim, a.scale_log2e, mrow, m_tile);
-                tmem_wait_ld(ra);
-                tmem_ld32(ts + 96, rb);
-                if (mode == 0) m_tile = chunk_max<0>(ra, 64, lim, a.scale_log2e, mrow, m_tile);
-                else if (mode == 1) m_tile = chunk_max<1>(ra, 64, lim, a.scale_log2e, mrow, m_tile);
-                else m_tile = chunk_max<2>(ra, 64, lim, a.scale_log2e, mrow, m_tile);
-                tmem_wait_ld(rb);
-                tmem_ld32(ts, ra); // pass 2 starts over at column 0
-                if (mode == 0) m_tile = chunk_max<0>(rb, 96, lim, a.scale_log2e, mrow, m_tile) * a.scale_log2e; // scale > 0 commutes with max
-                else if (mode == 1) m_tile = chunk_max<1>(rb, 96, lim, a.scale_log2e, mrow, m_tile);
-                else m_tile = chunk_max<2>(rb, 96, lim, a.scale_log2e, mrow, m_tile);
-
+                if (mode == 0) {
+                    // two independent chains: the maximum is a latency chain, not a throughput one
+                    m_tile = fmaxf(chunk_max<0>(ra, 0, lim, a.scale_log2e, mrow, m_tile), chunk_max<0>(rb, 32, lim, a.scale_log2e, mrow, m_tile));
+                    m_tile *= a.scale_log2e; // scale > 0 commutes with max
+                } else if (mode == 1) {
+                    m_tile = fmaxf(chunk_max<1>(ra, 0, lim, a.scale_log2e, mrow, m_tile), chunk_max<1>(rb, 32, lim, a.scale_log2e, mrow, m_tile));
+                } else {
+                    m_tile = fmaxf(chunk_max<2>(ra, 0, lim, a.scale_log2e, mrow, m_tile), chunk_max<2>(rb, 32, lim, a.scale_log2e, mrow, m_tile));
+                }
                 if (j == 0) {
                     m_used = fmaxf(m_tile, -1e30f);
                 } else {
                     const bool grow = m_tile > m_used + kRescaleThreshold;
                     if (__any_sync(0xffffffffu, grow)) {
                         // O_t must hold every product up to tile j-1 before it is rescaled
-                        ok = wait_bar(pv_done, (ct - 1u) & 1u, pb, a.status);
+                        ok = wait_bar(pv_done + ((ct - 1u) & 1u), ((ct - 1u) >> 1) & 1u, pb, a.status);
                         ok = __all_sync(0xffffffffu, ok);
                         if (!ok) break;
                         tc_fence_after();
@@ -747,7 +732,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         m_used = m_new;
                         l2.x *= alpha;
                         l2.y *= alpha;
-                        tmem_wait_ld(ra); // the pass-2 load issued above: one tcgen05.wait covers every load in flight
                         uint32_t o[32];
 #pragma unroll 1
                         for (int ch = 0; ch < 4; ++ch) {
@@ -760,25 +744,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         tmem_wait_st();
                     }
                 }
-                // ---- pass 2: P = exp2(x - m), row sum; each half of the row is handed to the tensor core as it is stored
                 const float neg_m = -m_used;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t(&cur)[32] = (c & 1) ? rb : ra;
-                    uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
-                    tmem_wait_ld(cur);
-                    if (c < 3) tmem_ld32(ts + (c + 1) * 32, nxt);
-                    uint32_t packed[16];
-                    if (mode == 0) chunk_exp<0, EMUL>(cur, c * 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
-                    else if (mode == 1) chunk_exp<1, EMUL>(cur, c * 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
-                    else chunk_exp<2, EMUL>(cur, c * 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
-                    tmem_st16(ts + c * 16, packed);
-                    if (c & 1) {
-                        tmem_wait_st();
-                        tc_fence_before();
-                        mbar_arrive(p_full + (c >> 1));
-                    }
-                }
+                uint32_t packed[16];
+                if (mode == 0) chunk_exp<0, EMUL>(ra, 0, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                else if (mode == 1) chunk_exp<1, EMUL>(ra, 0, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                else chunk_exp<2, EMUL>(ra, 0, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                tmem_st16(ts, packed);
+                if (mode == 0) chunk_exp<0, EMUL>(rb, 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                else if (mode == 1) chunk_exp<1, EMUL>(rb, 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                else chunk_exp<2, EMUL>(rb, 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                tmem_st16(ts + 16, packed);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(p_full + buf);
                 ++ct;
             }
             if (!ok) break;
@@ -940,6 +918,7 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     a.B = B; a.H = H; a.S = S; a.T = T;
     a.input_mode = p->input_mode;
     a.q = p->q; a.k = p->k; a.v = p->v;
+    a.row_stride = p->qkv_row_stride ? p->qkv_row_stride : H * D;
     a.act_scale = p->act_scale; a.q_w_scale = p->q_w_scale; a.k_w_scale = p->k_w_scale; a.v_w_scale = p->v_w_scale;
     a.freq_cis = p->freq_cis;
     a.rope_pos0 = p->rope_pos0;

@@ -19,7 +19,8 @@
 // same GPU (different streams, different host threads) would trample each other's partial results.
 // Issue calls to this entry point on one stream at a time per GPU.  The block keeps whatever the
 // previous call left; the part that has to start at zero (the arrival counters and the status
-// word) is cleared by a memset node at the head of each call.
+// word) is cleared by a memset node at the head of each call — which also means that such a call is always an
+// ordinary launch: the early-start levels need counters that are already zero without a memset in front.
 #include "../../include/flb_attn.h"
 
 #include <cuda_runtime.h>
@@ -67,4 +68,20 @@ extern "C" int flb_attn_decode_static_scratch(const flb_attn_params *p, void *cu
     if (st != FLB_OK) return st;
     q.scratch = ptr;
     return flb_attn_decode(&q, cuda_stream);
+}
+
+extern "C" int flb_attn_static_scratch_status(unsigned *status_out, void *cuda_stream) {
+    if (!status_out) return FLB_ERR_NULL_POINTER;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FLB_ERR_DEVICE;
+    void *ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_scratch_mutex);
+        ptr = g_scratch_ptr[dev];
+    }
+    if (!ptr) { // the entry point has not run on this GPU: nothing can have been reported
+        *status_out = 0u;
+        return FLB_OK;
+    }
+    return flb_attn_scratch_status(ptr, status_out, cuda_stream);
 }

@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define FLB_ATTN_ABI_VERSION 3
+#define FLB_ATTN_ABI_VERSION 4
 
 /* ---- status codes (0 = ok, negative = error) ------------------------------------ */
 typedef enum flb_status {
@@ -170,7 +170,7 @@ typedef struct flb_attn_params {
      * serialisation.  Its CTAs may then become resident while the previous kernel on the stream is still
      * draining; what they do before that kernel has completed (griddepcontrol.wait) depends on the level:
      *   1  fetch their first cache tiles.  Promise: the cache rows below each sequence's length and
-     *      past_lens were final BEFORE the previous kernel on the stream started.
+     *      past_lens were final BEFORE the previous kernel on the stream started (see the note on "final" below).
      *   2  in addition read q and k, rotate them and run the whole pass over the cached rows.  Promise,
      *      on top of level 1: q, k, act_scale, the weight scales and freq_cis were final before the
      *      previous kernel started — only v may still be in flight.  True in the decoder layer, where the
@@ -179,8 +179,20 @@ typedef struct flb_attn_params {
      * At both levels the new token's v, the cache append, the scratch and every output are touched only
      * after the previous kernel has completed, and the results are bit-identical to an ordinary launch.
      * Needs scratch_zeroed != 0 (a memset in front would serialise anyway); ignored otherwise.  A decode
-     * kernel launched this way also lets the next such call start early. */
+     * kernel launched this way also lets the next such call start early.
+     * "Final before the previous kernel started" means: every earlier writer of those buffers has COMPLETED.
+     * Stream order alone does not give that when the previous kernel was itself launched with programmatic
+     * serialisation (it may have started before ITS predecessor finished) — programmatic dependent launch is not
+     * transitive.  Level 1 is safe after any kernel that does not write the cache rows below the cached lengths;
+     * use level 2 only where the launch chain in front is known. */
     int early_start;
+
+    /* ABI version 4.  Elements between the rows of two consecutive tokens in q, k and v; 0 = head_num *
+     * size_per_head (dense [B,S,H,d]).  A larger value lets q, k and v be three column blocks of ONE
+     * [B*S, 3*H*d] buffer — the output of a single merged QKV projection in place of the reference's three GEMMs
+     * (open_decoder.cu:105-136): q = base, k = base + H*d, v = base + 2*H*d, qkv_row_stride = 3*H*d.  The byte
+     * stride must be a multiple of 16. */
+    int qkv_row_stride;
 } flb_attn_params;
 
 /* One exchange step between the ranks of a head-split layer (see out_peers above).  Every rank
@@ -275,9 +287,19 @@ int flb_attn_scratch_status(const void *scratch, unsigned *status_out, void *cud
  *   - The first call on each GPU looks the block's address up (not a stream operation): make that
  *     call before starting any stream capture on that GPU.
  *   - One block per GPU, shared by every call: calls that may overlap on a GPU race with each
- *     other; keep them on one stream.  The status word read by flb_attn_scratch_status() lives in
- *     the block and is not reachable through this entry point. */
+ *     other; keep them on one stream.
+ *   - The arrival counters in the block are cleared by a memset at the head of every call, so the call behaves as
+ *     if scratch_zeroed were 0: `early_start` is ignored (every call through this entry point is an ordinary
+ *     launch).
+ *   - The kernels' error word lives in the block too: read it with flb_attn_static_scratch_status().
+ *   - The block's address is looked up once per GPU and kept for the life of the process; a cudaDeviceReset()
+ *     invalidates it, so the library must not be used across one. */
 int flb_attn_decode_static_scratch(const flb_attn_params *p, void *cuda_stream);
+
+/* Error word of the calls made through flb_attn_decode_static_scratch() on the current GPU (same bits as
+ * flb_attn_scratch_status(): a bounded wait that ran out, a cached length outside [0, total_len-1]); 0 when that
+ * entry point has not been used on this GPU yet.  Synchronises the stream.  No counterpart in the reference. */
+int flb_attn_static_scratch_status(unsigned *status_out, void *cuda_stream);
 
 /* The reference's attention-output quantisation as a call of its own (launchAttnQuantizedTransposeKernel,
  * fasterLlama/cuda/decoder_kernels.cu:1179-1300, called at open_decoder.cu:245): attn fp32 [B,H,S,d] ->

@@ -51,7 +51,8 @@ struct HalfBits {
 inline float load_in(const flb_attn_params *p, const void *base, const float *w_scale, int b, int s,
                      int h, int i) {
     const int S = p->seq_len, H = p->head_num, d = p->size_per_head;
-    const size_t off = (((size_t)b * S + s) * H + h) * d + i;
+    const size_t row = p->qkv_row_stride ? (size_t)p->qkv_row_stride : (size_t)H * d; // elements between token rows
+    const size_t off = ((size_t)b * S + s) * row + (size_t)h * d + i;
     switch (p->input_mode) {
     case FLB_IN_INT32: {
         const float acc = (float)((const int32_t *)base)[off];

@@ -169,12 +169,15 @@ def main():
         t = torch.tensor([ms], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)  # the slowest rank's time
         ms = float(t.item())
+        push_used = bool(load(args.variant).e2e_tp_push_in_use()) if args.variant == "tp" else False
+        if args.variant == "tp":
+            load(args.variant).e2e_tp_finalize()  # unmaps the peers' exchange blocks, meets the other ranks, frees this rank's
         dist.barrier()
     if rank != 0:
         return
     np.savez(args.out, ids=ids, seq_len=sl, ms=ms)
     toks = cfg["batch"] * cfg["max_gen_len"]
-    push = bool(load(args.variant).e2e_tp_push_in_use()) if (args.variant == "tp" and world > 1) else False
+    push = push_used if (args.variant == "tp" and world > 1) else False
     print(json.dumps({"variant": args.variant, "tp": world, "tp_decode_exchange": ("peer stores" if push else ("nccl" if world > 1 else None)),
                       "config": args.config, "mask": args.mask, "cache_f16": bool(args.cache_f16),
                       "ms": round(ms, 2), "tokens_per_s": round(toks / ms * 1e3, 1), "first_ids": ids[0, :8].tolist(),

@@ -5,6 +5,9 @@
 // fasterLlama/decoding_sampling.h:9-33), constructs the reference's DecodingSampling and calls its
 // forward().  It is compiled together with the reference's four translation units, taken from a
 // patched copy of the reference checkout made by make_e2e_variants.py (which see for the patches).
+#ifdef FLB_WITH_NCCL
+#define FLB_OPEN_DECODER_TP_STATE // this translation unit holds the registration pointer of include/flb_open_decoder.h
+#endif
 #include <cublas_v2.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -13,8 +16,8 @@
 
 #include "decoding_sampling.h"
 #ifdef FLB_WITH_NCCL
-#define FLB_OPEN_DECODER_TP_STATE
 #include "flb_open_decoder.h"
+static flb_tp_ctx g_tp; // this rank's communicator block: owned by the program, registered before the decoder is built
 #endif
 
 extern "C" {
@@ -55,16 +58,20 @@ int e2e_tp_unique_id(char *out128) {
     return 0;
 }
 // 1 when the decode steps of the last run went through peer stores, 0 when they used ncclAllGather
-int e2e_tp_push_in_use(void) { return flb_tp_state.push_ready == 1 ? 1 : 0; }
+int e2e_tp_push_in_use(void) { return g_tp.push_ready == 1 ? 1 : 0; }
+// gives the exchange block back (every rank calls it, after its last run)
+int e2e_tp_finalize(void) {
+    if (g_tp.size > 1) flb_tp_push_teardown(&g_tp, 0);
+    return 0;
+}
 int e2e_tp_init(int rank, int size, int device, const char *id128) {
     cudaSetDevice(device);
     ncclUniqueId id;
     memcpy(&id, id128, sizeof(id));
     ncclComm_t comm;
     if (ncclCommInitRank(&comm, size, id, rank) != ncclSuccess) return 1;
-    flb_tp_state.comm = comm;
-    flb_tp_state.rank = rank;
-    flb_tp_state.size = size;
+    flb_tp_ctx_init(&g_tp, comm, rank, size);
+    flb_tp_register(&g_tp);
     return 0;
 }
 #endif
@@ -129,7 +136,7 @@ int e2e_run(const e2e_args *a, float *ms) {
     cudaError_t ce = cudaStreamSynchronize(stream);
 #ifdef FLB_WITH_NCCL
     // the decode steps' exchange kernels report a rank that did not show up through a sticky status word
-    const unsigned push_status = (ce == cudaSuccess) ? flb_tp_push_status(stream) : 0u;
+    const unsigned push_status = (ce == cudaSuccess) ? flb_tp_push_status(&g_tp, stream) : 0u;
 #else
     const unsigned push_status = 0u;
 #endif

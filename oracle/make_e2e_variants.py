@@ -17,7 +17,7 @@ reference is committed here; the copy lives under oracle/_ref/, which is git-ign
         the reference's own fp16 tensor-core rounding moves its sampled tokens.
 
 All are linked with oracle/e2e_runner.cu.  TEST / BASELINE INFRASTRUCTURE.
-usage: python oracle/make_e2e_variants.py [reference-root]"""
+usage: python oracle/make_e2e_variants.py <reference-root> [variants...]   (FLB_REFERENCE_ROOT also names the root)"""
 from __future__ import annotations
 
 import os
@@ -72,10 +72,23 @@ def patch_gemv(src: str) -> None:
     open(p, "w").write(t)
 
 
+def patch_ctx(src: str) -> None:
+    """The binding's per-object state: a flb_open_decoder_ctx member of OpenDecoder, initialised in its constructor."""
+    p = os.path.join(src, "open_decoder.h")
+    t = open(p).read()
+    t = _sub(t, r'#include "common.h"\n', '#include "common.h"\n#include "flb_open_decoder.h"\n', 1, "binding include")
+    t = _sub(t, r"(float \*ffn_inter_scale_buf_;[^\n]*\n)", r"\1        flb_open_decoder_ctx flb_ctx_;\n", 1, "ctx member")
+    open(p, "w").write(t)
+    p = os.path.join(src, "cuda", "open_decoder.cu")
+    t = open(p).read()
+    t = _sub(t, r"(\n        hidden_units_ = head_num_ \* size_per_head_;\n)", r"\1        flb_open_decoder_ctx_init(&flb_ctx_);\n", 1, "ctx init")
+    open(p, "w").write(t)
+
+
 def patch_quant_call(text: str) -> str:
     """The reference's own attention-output quantisation launch is skipped when the adaptor has done it."""
     return _sub(text, r"(\n\s*)launchAttnQuantizedTransposeKernel\(from_tensor_int8_buf_, qkv_buf_,",
-                r"\1if (!flb_open_decoder_fused_quant()) launchAttnQuantizedTransposeKernel(from_tensor_int8_buf_, qkv_buf_,", 1,
+                r"\1if (!flb_open_decoder_fused_quant(&flb_ctx_)) launchAttnQuantizedTransposeKernel(from_tensor_int8_buf_, qkv_buf_,", 1,
                 "optional fused quantisation")
 
 
@@ -83,14 +96,13 @@ def patch_adaptor(src: str) -> None:
     p = os.path.join(src, "cuda", "open_decoder.cu")
     lines = open(p).read().split("\n")
     s, e = attention_section(lines)
-    call = """            flb_open_decoder_attention(batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
-                                       query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
+    call = """            flb_open_decoder_attention(&flb_ctx_, batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
+                                       query_buf_, key_buf_, value_buf_, hidden_units_, from_tensor_scale_buf_,
                                        param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
                                        param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
                                        key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, from_tensor_int8_buf_, from_tensor_scale_buf_, param_.stream);"""
     lines[s:e] = call.split("\n")
     text = patch_quant_call("\n".join(lines))
-    text = text.replace('#include "open_decoder.h"', '#include "open_decoder.h"\n#include "flb_open_decoder.h"', 1)
     open(p, "w").write(text)
 
 
@@ -104,8 +116,8 @@ def patch_mix(src: str) -> None:
     s, e = attention_section(lines)
     head = """            static const int flb_use = getenv("FLB_E2E_USE") ? atoi(getenv("FLB_E2E_USE")) : 3;
             if ((seq_len > 1) ? (flb_use & 2) : (flb_use & 1)) {
-            flb_open_decoder_attention(batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
-                                       query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
+            flb_open_decoder_attention(&flb_ctx_, batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
+                                       query_buf_, key_buf_, value_buf_, hidden_units_, from_tensor_scale_buf_,
                                        param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
                                        param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
                                        key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, from_tensor_int8_buf_, from_tensor_scale_buf_, param_.stream);
@@ -118,8 +130,8 @@ def patch_mix(src: str) -> None:
                 std::vector<float> h_ref(n), h_flb(n);
                 cudaStreamSynchronize(param_.stream);
                 cudaMemcpy(h_ref.data(), qkv_buf_, n * sizeof(float), cudaMemcpyDeviceToHost);
-                flb_open_decoder_attention(batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
-                                       query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
+                flb_open_decoder_attention(&flb_ctx_, batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
+                                       query_buf_, key_buf_, value_buf_, hidden_units_, from_tensor_scale_buf_,
                                        param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
                                        param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
                                        key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, from_tensor_int8_buf_, from_tensor_scale_buf_, param_.stream);
@@ -134,7 +146,6 @@ def patch_mix(src: str) -> None:
     lines[s:e] = head.split("\n") + lines[s:e] + tail.split("\n")
     text = "\n".join(lines)
     text = text.replace('#include "open_decoder.h"', '#include <vector>\n#include <cmath>\n#include "open_decoder.h"', 1)
-    text = text.replace('#include "open_decoder.h"', '#include "open_decoder.h"\n#include "flb_open_decoder.h"', 1)
     open(p, "w").write(text)
 
 
@@ -143,7 +154,7 @@ def patch_tp(src: str) -> None:
     through flb_open_decoder_attention_tp (which all-gathers the head outputs); the rest of the layer is untouched."""
     p = os.path.join(src, "cuda", "open_decoder.cu")
     text = open(p).read()
-    text = _sub(text, r"(int k = hidden_units_;\n)", r"\1            const int n_tp = n / flb_tp_size();\n            const int tp_col0 = flb_tp_rank() * n_tp;\n", 1, "tp slice")
+    text = _sub(text, r"(int k = hidden_units_;\n)", r"\1            const int n_tp = n / flb_tp_size(&flb_ctx_);\n            const int tp_col0 = flb_tp_rank(&flb_ctx_) * n_tp;\n", 1, "tp slice")
     for x in ("query", "key", "value"):
         text = _sub(text,
                     rf"n, m, k,(\s*)&weight_alpha,(\s*)param_\.attention\.{x}_weight\.kernel, weight_Traits_::AType, n,(\s*)from_tensor_int8_buf_, weight_Traits_::BType, k,(\s*)&weight_beta,(\s*){x}_buf_, weight_Traits_::CType, n,",
@@ -158,7 +169,7 @@ def patch_tp(src: str) -> None:
             e = i - 2
     if s is None or e is None or lines[s].strip() != "/**" or lines[e - 1].strip() != "}":
         raise RuntimeError("attention section anchors not found")
-    call = """            flb_open_decoder_attention_tp(batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
+    call = """            flb_open_decoder_attention_tp(&flb_ctx_, batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,
                                           query_buf_, key_buf_, value_buf_, from_tensor_scale_buf_,
                                           param_.attention.query_weight.weight_scale, param_.attention.key_weight.weight_scale,
                                           param_.attention.value_weight.weight_scale, freq_cis, param_.attn_mask,
@@ -166,7 +177,6 @@ def patch_tp(src: str) -> None:
                                           param_.stream);"""
     lines[s:e] = call.split("\n")
     text = patch_quant_call("\n".join(lines))
-    text = text.replace('#include "open_decoder.h"', '#include "open_decoder.h"\n#include "flb_open_decoder.h"', 1)
     open(p, "w").write(text)
 
 
@@ -189,6 +199,8 @@ def build(name: str, ref_root: str) -> str:
         patch_tp(src)
     else:
         patch_adaptor(src)
+    if name in ("flb", "mix", "tp"):
+        patch_ctx(src)  # after the section patches: those address open_decoder.cu by line number
     if name == "ref32":
         p = os.path.join(src, "cuda", "common.h")
         t = open(p).read()
@@ -214,7 +226,10 @@ def build(name: str, ref_root: str) -> str:
     return lib
 
 
-def main(ref_root: str = "/root/reference") -> None:
+def main(ref_root: str | None = None) -> None:
+    ref_root = ref_root or os.environ.get("FLB_REFERENCE_ROOT")
+    if not ref_root or not os.path.isdir(os.path.join(ref_root, "fasterLlama")):
+        raise SystemExit("usage: make_e2e_variants.py <reference checkout> [variants...]  (or set FLB_REFERENCE_ROOT)")
     os.makedirs(OUT, exist_ok=True)
     for name in (sys.argv[2:] or ["ref", "flb", "ref32", "mix", "tp"]):
         print("built", build(name, ref_root))

@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_lib.EXPORTS), (declared ^ set(_lib.EXPORTS))
     for name in declared:
         assert hasattr(lib, name)
-    assert lib.flb_attn_abi_version() == 3
+    assert lib.flb_attn_abi_version() == 4
 
 
 def test_missing_library_fails_loudly(tmp_path):
