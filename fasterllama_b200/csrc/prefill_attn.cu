@@ -341,36 +341,35 @@ __device__ __forceinline__ bool sched_read(PrefillBarriers *pb, unsigned *status
 }
 __device__ __forceinline__ void sched_release(PrefillBarriers *pb, uint32_t count) { mbar_arrive(&pb->sched_empty[count % SCHED_DEPTH]); }
 
-// One 128-key score tile of one query row: row maximum, P = 2^(x - m) written back as fp16 pairs over the columns
-// the scores came from (keys 2c, 2c+1 in column c), row sum.  MODE 0: every key visible, x = s * scale; MODE 1:
-// keys [0, lim) visible (causal diagonal / end of the prompt); MODE 2: additionally the caller's additive mask.
-// EMUL > 0: every EMUL-th exponential is evaluated on the FMA pipe instead of the special-function unit.
-template <int MODE> __device__ __forceinline__ float score_of(uint32_t raw, int idx, int lim, float scale, const float *mrow) {
-    if (MODE == 0) return __uint_as_float(raw);
-    if (MODE == 1) return (idx < lim) ? __uint_as_float(raw) * scale : -INFINITY;
-    return (idx < lim) ? fmaf(__ldg(mrow + idx), kLog2e, __uint_as_float(raw) * scale) : -INFINITY;
-}
-template <int MODE> __device__ __forceinline__ float chunk_max(const uint32_t (&r)[32], int base, int lim, float scale, const float *mrow, float m) {
+// Softmax arithmetic on 32 scores of one query row held in registers.  A tile that needs masking is brought into the
+// common form first (mask_chunk: the scaled score plus the mask value, or -inf, written back over the raw score, and
+// the scale set to 1), so that the maximum and the exponentials exist once in the kernel: what the sixteen warps'
+// different roles execute has to fit the SM's instruction cache together (measured: the same kernel with each masked
+// form expanded separately, 83 KB of code instead of 52 KB, ran 12 % slower).
+// GENERIC: the caller's additive mask row; otherwise keys [0, lim) are visible (causal diagonal / end of the prompt).
+template <bool GENERIC> __device__ __forceinline__ void mask_chunk(uint32_t (&r)[32], int base, int lim, float scale, const float *mrow) {
 #pragma unroll
-    for (int i = 0; i < 32; i += 2)
-        m = max3(m, score_of<MODE>(r[i], base + i, lim, scale, mrow), score_of<MODE>(r[i + 1], base + i + 1, lim, scale, mrow));
+    for (int i = 0; i < 32; ++i) {
+        float x = -INFINITY;
+        if (base + i < lim) x = GENERIC ? fmaf(__ldg(mrow + base + i), kLog2e, __uint_as_float(r[i]) * scale) : __uint_as_float(r[i]) * scale;
+        r[i] = __float_as_uint(x);
+    }
+}
+__device__ __forceinline__ float chunk_max(const uint32_t (&r)[32], float m) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) m = max3(m, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
     return m;
 }
-template <int MODE, int EMUL>
-__device__ __forceinline__ void chunk_exp(const uint32_t (&r)[32], int base, int lim, float scale, const float *mrow, float neg_m,
-                                          float2 &l2, uint32_t (&packed)[16]) {
+// P = 2^(x * scale - m) as fp16 pairs, row sum.  EMUL > 0: every EMUL-th exponential on the FMA pipe instead of the
+// special-function unit.
+template <int EMUL>
+__device__ __forceinline__ void chunk_exp(const uint32_t (&r)[32], float scale, float neg_m, float2 &l2, uint32_t (&packed)[16]) {
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-        float2 y;
-        if (MODE == 0) {
-            y = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), make_float2(scale, scale),
-                           make_float2(neg_m, neg_m));
-        } else {
-            y = __fadd2_rn(make_float2(score_of<MODE>(r[i], base + i, lim, scale, mrow), score_of<MODE>(r[i + 1], base + i + 1, lim, scale, mrow)),
-                           make_float2(neg_m, neg_m));
-        }
-        float2 p;
+        const float2 y = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), make_float2(scale, scale),
+                                    make_float2(neg_m, neg_m));
         constexpr int E = EMUL > 0 ? EMUL : 1;
+        float2 p;
         p.x = (EMUL > 0 && (i % E) == E - 1) ? ex2_fma(y.x) : ex2(y.x);
         p.y = (EMUL > 0 && ((i + 1) % E) == E - 1) ? ex2_fma(y.y) : ex2(y.y);
         l2 = __fadd2_rn(l2, p);
@@ -707,16 +706,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (mode == 2 && row >= a.S) lim = 0; // rows beyond the prompt: no mask row to read
                 const float *mrow = (mode == 2) ? a.attn_mask + (size_t)min(row, a.S - 1) * a.mask_row_stride + k0 : nullptr;
                 tmem_wait_ld(ra, rb);
-                float m_tile = -INFINITY;
-                if (mode == 0) {
-                    // two independent chains: the maximum is a latency chain, not a throughput one
-                    m_tile = fmaxf(chunk_max<0>(ra, 0, lim, a.scale_log2e, mrow, m_tile), chunk_max<0>(rb, 32, lim, a.scale_log2e, mrow, m_tile));
-                    m_tile *= a.scale_log2e; // scale > 0 commutes with max
-                } else if (mode == 1) {
-                    m_tile = fmaxf(chunk_max<1>(ra, 0, lim, a.scale_log2e, mrow, m_tile), chunk_max<1>(rb, 32, lim, a.scale_log2e, mrow, m_tile));
-                } else {
-                    m_tile = fmaxf(chunk_max<2>(ra, 0, lim, a.scale_log2e, mrow, m_tile), chunk_max<2>(rb, 32, lim, a.scale_log2e, mrow, m_tile));
+                float sc = a.scale_log2e;
+                if (mode != 0) { // rare: the causal diagonal, the end of the prompt, or a caller-supplied mask
+                    if (mode == 1) {
+                        mask_chunk<false>(ra, 0, lim, sc, mrow);
+                        mask_chunk<false>(rb, 32, lim, sc, mrow);
+                    } else {
+                        mask_chunk<true>(ra, 0, lim, sc, mrow);
+                        mask_chunk<true>(rb, 32, lim, sc, mrow);
+                    }
+                    sc = 1.0f;
                 }
+                // two independent chains: the maximum is a latency chain, not a throughput one; scale > 0 commutes with max
+                const float m_tile = fmaxf(chunk_max(ra, -INFINITY), chunk_max(rb, -INFINITY)) * sc;
                 if (j == 0) {
                     m_used = fmaxf(m_tile, -1e30f);
                 } else {
@@ -746,13 +748,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 }
                 const float neg_m = -m_used;
                 uint32_t packed[16];
-                if (mode == 0) chunk_exp<0, EMUL>(ra, 0, lim, a.scale_log2e, mrow, neg_m, l2, packed);
-                else if (mode == 1) chunk_exp<1, EMUL>(ra, 0, lim, a.scale_log2e, mrow, neg_m, l2, packed);
-                else chunk_exp<2, EMUL>(ra, 0, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                chunk_exp<EMUL>(ra, sc, neg_m, l2, packed);
                 tmem_st16(ts, packed);
-                if (mode == 0) chunk_exp<0, EMUL>(rb, 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
-                else if (mode == 1) chunk_exp<1, EMUL>(rb, 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
-                else chunk_exp<2, EMUL>(rb, 32, lim, a.scale_log2e, mrow, neg_m, l2, packed);
+                chunk_exp<EMUL>(rb, sc, neg_m, l2, packed);
                 tmem_st16(ts + 16, packed);
                 tmem_wait_st();
                 tc_fence_before();
