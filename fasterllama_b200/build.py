@@ -74,7 +74,7 @@ def build_reference(force: bool = False) -> str | None:
     return out
 
 
-E2E_VARIANTS = ("ref", "flb", "ref32", "mix", "tp")
+E2E_VARIANTS = ("ref", "flb", "ref32", "mix", "tp", "opt")
 
 
 def build_e2e_variants(force: bool = False) -> list[str]:

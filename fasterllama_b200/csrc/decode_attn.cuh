@@ -8,6 +8,8 @@ namespace flb {
 
 constexpr int kHeadDim = 128;          // size_per_head this build is specialised for
 constexpr int kDefaultSplitLen = 512;  // cache rows per split-KV partition
+constexpr int kShortSlabRows = 1024;   // slabs of at most this many rows ...
+constexpr int kShortSlabSplitLen = 256; // ... are split into partitions of this many rows
 constexpr int kStatusWords = 4;        // status header (16 B) in front of the arrival counters
 
 // Error bits a kernel may set in the status word (scratch[0]).

@@ -14,24 +14,26 @@
 //    copies of Q (and of K,V when the cache is fp32) for the tensor cores.
 //
 // 2. flb_prefill_attn_kernel — flash attention on the 5th-generation tensor cores, one persistent CTA of 16
-//    warps per SM.  A work item is 256 query rows of one (b,h) (two 128-row tiles); items are handed out through
-//    an atomic counter, heavy (late) query blocks first, in groups of heads whose K/V stay in L2.  K/V tiles
-//    hold 128 keys.  TMEM (512 columns): S0, S1 (fp32 scores of the two query tiles; P overwrites them as fp16
-//    pairs) and O0, O1 (fp32 accumulators).  Warp roles:
-//      warp 0      work scheduler + K loader: TMA boxes (128-byte swizzle) into a ring; a stage is free again
-//                  once both query tiles' S = Q.K^T over it have been computed
-//      warp 1      allocates TMEM and issues tcgen05.mma in the order PV0_j, S0_{j+1}, PV1_j, S1_{j+1}: while
-//                  one query tile's scores go through the softmax warps the tensor pipe works on the other's.
-//                  S is an SS form (both operands in shared memory, 128 x 128 x 16 per instruction), P.V reads
-//                  P from TMEM as the A operand and V from shared memory as an MN-major B operand.  At an item
-//                  boundary the next item's first S takes the place of S_{j+1}: the pipe never drains.
-//      warp 2      V loader (its own ring: a stage is free again once both P.V products have retired)
-//      warp 3      Q loader: a query tile's buffer is refilled as soon as its last S of the item has retired
-//      warps 4-7   softmax of query tile 0, one thread per row: two passes over the 128 scores in TMEM (row
-//      warps 8-11  maximum, then P = 2^(x - m) and the row sum), 32 columns in flight while 32 are worked on;
-//      (tile 1)    the keys 0..63 half of P is handed to the tensor core before the second half is computed; O is
-//                  rescaled only when a row's maximum grew by more than 2^8 (exact: the final division uses
-//                  the same reference maximum); a share of the exponentials runs on the FMA pipe
+//    warps per SM.  A work item is 256 query rows of one (b,h) (two 128-row query tiles); items are handed out through
+//    an atomic counter, heavy (late) query blocks first, in groups of heads whose K/V stay in L2.  Key tiles hold 64
+//    keys.  TMEM (512 columns): per query tile two score buffers of 64 columns (fp32 scores; P overwrites them as
+//    fp16 pairs) and 128 columns of fp32 accumulator O.  Warp roles:
+//      warp 0      work scheduler + K/V loader: TMA boxes (128-byte swizzle) into one ring whose stage holds the K
+//                  tile and the V tile of the same 64 keys; a stage is free again once both query tiles' P.V over
+//                  it have retired
+//      warps 1, 3  issue S = Q_t.K_j^T for query tile 0 / 1 (SS form: both operands in shared memory, 128 x 64 x 16
+//                  per instruction) and load that tile's query rows.  S runs TWO key tiles ahead of P.V: while
+//                  the softmax threads work on S_j, S_{j+1} is already in TMEM, so they never wait for the pipe;
+//                  S_{j+2} overwrites the buffer P_j occupied and is issued once P_j.V_j has retired
+//      warp 2      issues every O_t += P_j.V_j (P read from TMEM as the A operand, V from shared memory as an
+//                  MN-major B operand).  tcgen05.mma is issued by single threads, and one thread cannot issue, wait
+//                  and commit fast enough for the pipe: three do it.  The tile stream runs across work items
+//                  (the next item's first two S are issued while the current item's last products retire).
+//      warps 4-7   softmax of query tile 0, one thread per row: load the 64 scores of a key tile, maximum,
+//      warps 8-11  P = 2^(x - m) and the row sum, P stored over the scores, buffer handed to warp 2; O is rescaled
+//      (tile 1)    only when a row's maximum grew by more than 2^8 (exact: the final division uses the same
+//                  reference maximum).  Masked tiles are first brought into the unmasked form, so that the
+//                  arithmetic exists once: the kernel's instruction footprint is a first-order cost here
 //      warps 12-15 epilogue: O_t / l from TMEM to global memory while the other warps are on the next item
 //    All hand-offs are mbarriers (TMA transaction counts, tcgen05.commit, thread arrivals); every
 //    wait is bounded by a wall-clock budget and reports through the status word instead of hanging.
@@ -259,16 +261,8 @@ struct __align__(8) PrefillBarriers {
     int sched_bh[SCHED_DEPTH], sched_qb[SCHED_DEPTH]; // the published items; bh < 0 = no more work
     uint32_t tmem_base;
     int abort_flag;
-#ifdef FLB_PF_TRACE
-    uint32_t tr_clk[176];
-    unsigned short tr_code[176];
-#endif
 };
-#ifdef FLB_PF_TRACE
-constexpr int kBarrierSlot = 512 + 1056;
-#else
 constexpr int kBarrierSlot = 512;
-#endif
 constexpr size_t kPrefillSmem = 2 * (size_t)TILE_BYTES + (size_t)KV_STAGES * STAGE_BYTES + 2 * BM * sizeof(float) + kBarrierSlot;
 static_assert(sizeof(PrefillBarriers) <= kBarrierSlot, "barrier block must fit its slot");
 static_assert(kPrefillSmem <= 232448, "exceeds the 227 KB a CTA may use");
@@ -300,14 +294,6 @@ __device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, Prefill
     return wait_bar_slow(bar, parity, pb, status);
 }
 
-#ifdef FLB_PF_TRACE
-// TEMPORARY tuning aid: SM clock stamps of CTA 0's MMA-issuing thread, kept in shared memory (cheap) and dumped
-// into the (unused with an fp16 cache) K staging area when the kernel ends.
-#define TRACE_MAX 176
-#define TR(code) do { if (blockIdx.x == 0 && (code) < 0x200 && tr_on && tr_n < TRACE_MAX) { uint32_t c_; asm volatile("mov.u32 %0, %%clock;" : "=r"(c_)); pb->tr_clk[tr_n] = c_; pb->tr_code[tr_n] = (unsigned short)(code); ++tr_n; } } while (0)
-#else
-#define TR(code) do { } while (0)
-#endif
 
 // A work item is 256 query rows of one (b,h): two 128-row tiles, each with its own S/P and O columns in TMEM.
 struct ItemGeom {
@@ -533,10 +519,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             uint32_t taken = 0, kt = 0, gs = 0, nq = 0; // items read, ring tiles passed, S issued, query tiles loaded
             int nmax = 0, n_t = 0, j = 0;
             bool ok = true, valid = true;
-#ifdef FLB_PF_TRACE
-            uint32_t tr_n = 0, tr_iter = 0;
-            bool tr_on = false;
-#endif
             while (ok && valid) {
                 if (j == nmax) {
                     // ---- next work item: its query rows go into the tile's buffer as soon as the previous item's
@@ -569,15 +551,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     ++j;
                     continue;
                 }
-#ifdef FLB_PF_TRACE
-                tr_on = (t == 0) && (++tr_iter >= FLB_PF_TRACE);
-                TR(0x1f0);
-#endif
                 if (j == 0) ok = wait_bar(q_full, (nq - 1u) & 1u, pb, a.status);
                 const uint32_t buf = gs & 1u;
                 if (ok && gs >= 2) ok = wait_bar(pv_done + buf, ((gs - 2u) >> 1) & 1u, pb, a.status); // P_{j-2}.V_{j-2} has read this buffer
                 if (!ok) break;
-                TR(0x107);
                 tc_fence_after();
                 const uint64_t dk = dk0 + (uint64_t)(ks * (uint32_t)(STAGE_BYTES >> 4));
                 const uint32_t ts = tS_t + buf * (uint32_t)BN;
@@ -589,17 +566,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 }
                 umma_commit(s_full + buf);
                 if (j == n_t - 1) umma_commit(q_empty); // the query tile's buffer may take the next item's rows
-                TR(0x108);
                 ++gs;
                 ++j;
             }
-#ifdef FLB_PF_TRACE
-            if (blockIdx.x == 0 && t == 0) {
-                uint64_t *dst = reinterpret_cast<uint64_t *>(a.kh);
-                dst[0] = tr_n;
-                for (uint32_t i = 0; i < tr_n; ++i) dst[1 + i] = ((uint64_t)pb->tr_code[i] << 32) | pb->tr_clk[i];
-            }
-#endif
         }
         __syncwarp();
     } else if (warp == 2) {

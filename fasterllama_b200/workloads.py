@@ -164,6 +164,12 @@ def to_device(case: Case, device: str = "cuda:0") -> dict[str, Any]:
     import torch
 
     dev = {k: torch.from_numpy(np.ascontiguousarray(v)).to(device) for k, v in case.arrays.items()}
+    if "_merged" in case.arrays:
+        # q, k, v are column blocks of one [B, S, row] buffer (a merged QKV projection's output): keep that layout
+        B, S, H, d = case.arrays["q"].shape
+        buf = dev["_merged"]
+        for i, name in enumerate(("q", "k", "v")):
+            dev[name] = buf[:, :, i * H * d:(i + 1) * H * d].unflatten(2, (H, d))
     n = A.workspace_bytes(case.B, case.H, case.T, case.S, case.split_len)
     dev["scratch"] = torch.empty(n, dtype=torch.uint8, device=device)
     return dev

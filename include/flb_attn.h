@@ -139,8 +139,8 @@ typedef struct flb_attn_params {
     size_t scratch_bytes;
     int scratch_zeroed;
 
-    /* rows of one split-KV partition; 0 = default (512).  Results depend on this value
-     * and on each sequence's own length only — never on B, H, the GPU count or the grid. */
+    /* rows of one split-KV partition; 0 = default (512; 256 when total_len <= 1024).  Results depend on this
+     * value and on each sequence's own length only — never on B, H, the GPU count or the grid. */
     int split_len;
 
     /* Optional fused epilogue (both NULL = off): the reference's next step,

@@ -33,6 +33,8 @@
  *                     kernel was itself launched with programmatic serialisation (a library GEMM may be), so
  *                     level 2 is opt-in for callers who know their launch chain.
  *   FLB_TP_PUSH=0     tensor-parallel form only: decode steps use ncclAllGather instead of peer stores
+ *   FLB_MERGED_QKV=1  one INT8 GEMM for the Q, K and V projections (flb_open_decoder_packed_qkv below); q, k and v are then
+ *                     column blocks of one int32 buffer and the attention call reads them in place
  *   FLB_FUSE_QUANT=1  also do the step that follows attention (launchAttnQuantizedTransposeKernel,
  *                     open_decoder.cu:245-246) inside the call; the caller then skips its own launch:
  *                         if (!flb_open_decoder_fused_quant(&flb_ctx_)) launchAttnQuantizedTransposeKernel(...);
@@ -51,6 +53,8 @@
 
 struct flb_tp_ctx;
 
+#define FLB_OPEN_DECODER_MAX_LAYERS 128
+
 typedef struct flb_open_decoder_ctx {
     /* switches (environment, read once per object) */
     int cache_f16;
@@ -67,6 +71,14 @@ typedef struct flb_open_decoder_ctx {
     cudaStream_t clean_stream;
     /* tensor-parallel form: the communicator block this decoder uses (NULL: single GPU) */
     struct flb_tp_ctx *tp;
+    /* merged QKV projection (FLB_MERGED_QKV=1): per layer, the caller's three [hidden, hidden] INT8 weight matrices
+     * packed once into one [hidden, 3*hidden] matrix, found again by the query matrix's address */
+    int merged_qkv;
+    int n_packed;
+    struct {
+        const int8_t *wq, *wk, *wv;
+        int8_t *packed;
+    } packed[FLB_OPEN_DECODER_MAX_LAYERS];
 } flb_open_decoder_ctx;
 
 static inline int flb_open_decoder_env_int(const char *name, int fallback) {
@@ -88,6 +100,7 @@ static inline void flb_open_decoder_ctx_init(flb_open_decoder_ctx *c) {
     c->early_start = 0;
 #endif
     c->fused_quant = flb_open_decoder_env_int("FLB_FUSE_QUANT", 0);
+    c->merged_qkv = flb_open_decoder_env_int("FLB_MERGED_QKV", 0);
     c->mask_mode = -1;
 #ifdef FLB_WITH_NCCL
     c->tp = flb_tp_default();
@@ -95,6 +108,46 @@ static inline void flb_open_decoder_ctx_init(flb_open_decoder_ctx *c) {
 }
 
 static inline int flb_open_decoder_fused_quant(const flb_open_decoder_ctx *c) { return c->fused_quant; }
+
+/* Releases what the context owns (the packed weight copies).  OpenDecoder::~OpenDecoder calls it. */
+static inline void flb_open_decoder_ctx_destroy(flb_open_decoder_ctx *c) {
+    for (int i = 0; i < c->n_packed; ++i) cudaFree(c->packed[i].packed);
+    c->n_packed = 0;
+}
+
+/* Merged QKV projection (the three cublasGemmEx calls of open_decoder.cu:105-136 as one): returns the layer's
+ * [hidden, 3*hidden] INT8 weight matrix — the caller's three row-major [in, out] matrices side by side — packing it on
+ * the stream the first time this layer's matrices are seen, or NULL when merging is off or no copy can be made (the
+ * caller then issues its three GEMMs as before).  One GEMM  C[m, 3*hidden] = X[m, hidden] . W  then leaves q, k and v
+ * as column blocks of ONE int32 buffer, which the attention call reads in place (qkv_row_stride = 3 * hidden).
+ * The copies live until flb_open_decoder_ctx_destroy(); the caller's matrices must not change once packed. */
+static inline const int8_t *flb_open_decoder_packed_qkv(flb_open_decoder_ctx *c, const int8_t *wq, const int8_t *wk, const int8_t *wv,
+                                                        int hidden, cudaStream_t stream) {
+    if (!c->merged_qkv) return NULL;
+    for (int i = 0; i < c->n_packed; ++i)
+        if (c->packed[i].wq == wq && c->packed[i].wk == wk && c->packed[i].wv == wv) return c->packed[i].packed;
+    if (c->n_packed >= FLB_OPEN_DECODER_MAX_LAYERS) return NULL;
+    int8_t *dst = NULL;
+    const size_t n = (size_t)hidden;
+    if (cudaMalloc((void **)&dst, 3 * n * n) != cudaSuccess) {
+        cudaGetLastError();
+        return NULL;
+    }
+    const int8_t *src[3] = {wq, wk, wv};
+    for (int i = 0; i < 3; ++i) {
+        if (cudaMemcpy2DAsync(dst + i * n, 3 * n, src[i], n, n, n, cudaMemcpyDeviceToDevice, stream) != cudaSuccess) {
+            cudaFree(dst);
+            cudaGetLastError();
+            return NULL;
+        }
+    }
+    c->packed[c->n_packed].wq = wq;
+    c->packed[c->n_packed].wk = wk;
+    c->packed[c->n_packed].wv = wv;
+    c->packed[c->n_packed].packed = dst;
+    ++c->n_packed;
+    return dst;
+}
 
 /* attn_q8 / attn_q8_scale: from_tensor_int8_buf_ / from_tensor_scale_buf_ (used when FLB_FUSE_QUANT=1; the scale
  * buffer may be the same memory as from_tensor_scale_buf_ passed as the activation scale: every read of a row's

@@ -81,7 +81,10 @@ def tp_init(variant: str):
     return rank, world, local
 
 
-def run(variant: str, cfg: dict, mask: str = "inclusive", device: int = 0):
+def run(variant: str, cfg: dict, mask: str = "inclusive", device: int = 0, forced_ids=None, want_logits: bool = False):
+    """One generation run.  forced_ids: int32 [steps, batch] on the device — every step's sampled ids are replaced by
+    these (teacher forcing with another run's ids).  want_logits: also returns every step's logits row as the sampler
+    read it, float32 [steps, batch, vocab] on the device (else None)."""
     lib = load(variant)
     dev = f"cuda:{device}"
     g = torch.Generator(device=dev)
@@ -134,22 +137,62 @@ def run(variant: str, cfg: dict, mask: str = "inclusive", device: int = 0):
     a.prompt_tokens, a.prompt_mask = prompts.data_ptr(), pmask.data_ptr()
     a.final_gamma, a.lm_head = fg.data_ptr(), head.data_ptr()
     a.output_ids, a.seq_len = out_ids.data_ptr(), seq_len.data_ptr()
+    steps = cfg["max_gen_len"]
+    logits = torch.zeros((steps, B, cfg["vocab"]), dtype=torch.float32, device=dev) if want_logits else None
+    lib.e2e_set_probe.argtypes = [C.c_void_p, C.c_void_p]
+    lib.e2e_set_probe.restype = None
+    lib.e2e_set_probe(logits.data_ptr() if want_logits else None, forced_ids.data_ptr() if forced_ids is not None else None)
     ms = C.c_float(0)
     st = lib.e2e_run(C.byref(a), C.byref(ms))
     torch.cuda.synchronize()
+    lib.e2e_set_probe(None, None)
     if st != 0:
         raise RuntimeError(f"e2e_run status {st}")
+    if want_logits:
+        return out_ids.cpu().numpy(), seq_len.cpu().numpy(), float(ms.value), logits
     return out_ids.cpu().numpy(), seq_len.cpu().numpy(), float(ms.value)
+
+
+def compare_logits(variants: list[str], cfg: dict, mask: str = "inclusive", device: int = 0) -> dict:
+    """Teacher-forced comparison at the level of the sampler's input: the first variant runs freely; every other variant is
+    fed the first one's ids at every step, so all of them see the same token history, and each step's logits row is
+    compared with the first variant's.  Per variant: the largest |difference| of a logit, the fraction of (step, sequence)
+    pairs whose top-4 SET (what top-k = 4 sampling draws from) and whose arg-max are the same, and the largest difference
+    relative to the spread of the row's top-4 values."""
+    dev = f"cuda:{device}"
+    ids0, sl0, _, base = run(variants[0], cfg, mask, device, want_logits=True)
+    steps, B = cfg["max_gen_len"], cfg["batch"]
+    forced = torch.from_numpy(np.ascontiguousarray(ids0[:, :steps].T)).to(dev)  # word_ids rows are [step][batch]
+    top0 = base.topk(4, dim=-1)
+    out = {"reference_variant": variants[0], "steps": steps, "batch": B, "max_abs_logit": float(base[torch.isfinite(base) & (base.abs() < 1e30)].abs().max())}
+    for v in variants[1:]:
+        _, _, _, lg = run(v, cfg, mask, device, forced_ids=forced, want_logits=True)
+        ok = (base.abs() < 1e30) & (lg.abs() < 1e30)  # finished sequences carry +-FLT_MAX rows
+        diff = torch.where(ok, (lg - base).abs(), torch.zeros_like(lg))
+        top = lg.topk(4, dim=-1)
+        same_set = (top.indices.sort(dim=-1).values == top0.indices.sort(dim=-1).values).all(dim=-1)
+        same_arg = top.indices[..., 0] == top0.indices[..., 0]
+        gap = (top0.values[..., 3] - base.topk(5, dim=-1).values[..., 4]).clamp_min(1e-12)  # what separates the 4th from the 5th candidate
+        per_step = diff.amax(dim=(1, 2))
+        out[v] = {"max_abs_diff": float(diff.max()), "mean_abs_diff": float(diff.mean()),
+                  "max_abs_diff_first_step": float(per_step[0]), "max_abs_diff_last_step": float(per_step[-1]),
+                  "top4_set_same": float(same_set.float().mean()), "argmax_same": float(same_arg.float().mean()),
+                  "steps_with_all_top4_sets_same": float(same_set.all(dim=1).float().mean()),
+                  "median_4th_to_5th_gap": float(gap.median())}
+        del lg
+    return out
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--variant", required=True, choices=["ref", "flb", "ref32", "mix", "tp"])
+    ap.add_argument("--variant", required=True, choices=["ref", "flb", "ref32", "mix", "tp", "opt"])
+    ap.add_argument("--compare-logits", default="", help="comma-separated variants: run --variant freely, feed its ids to these and compare every step's logits with it")
     ap.add_argument("--config", default="small", choices=sorted(CONFIGS))
     ap.add_argument("--out", required=True)
     ap.add_argument("--mask", default="inclusive", choices=["inclusive", "strict"])
     ap.add_argument("--cache-f16", action="store_true")
     ap.add_argument("--fuse-quant", action="store_true", help="adaptor also does the attention-output quantisation")
+    ap.add_argument("--merged-qkv", action="store_true", help="opt: one INT8 GEMM for the Q, K and V projections")
     ap.add_argument("--no-push", action="store_true", help="tp: decode steps use ncclAllGather instead of peer stores")
     ap.add_argument("--repeat", type=int, default=1, help="runs; the time of the last one is reported")
     args = ap.parse_args()
@@ -159,7 +202,14 @@ def main():
         os.environ["FLB_FUSE_QUANT"] = "1"
     if args.no_push:
         os.environ["FLB_TP_PUSH"] = "0"
+    if args.merged_qkv:
+        os.environ["FLB_MERGED_QKV"] = "1"
     cfg = CONFIGS[args.config]
+    if args.compare_logits:
+        res = compare_logits([args.variant] + [v for v in args.compare_logits.split(",") if v], cfg, mask=args.mask)
+        res["config"] = args.config
+        print(json.dumps(res))
+        return
     rank, world, local = tp_init(args.variant)
     for _ in range(args.repeat):
         ids, sl, ms = run(args.variant, cfg, mask=args.mask, device=local)
@@ -176,6 +226,13 @@ def main():
     if rank != 0:
         return
     np.savez(args.out, ids=ids, seq_len=sl, ms=ms)
+    if args.variant == "mix":
+        lib = load("mix")
+        mx = (C.c_double * 4).in_dll(lib, "flb_e2e_mix_max")
+        calls = (C.c_long * 3).in_dll(lib, "flb_e2e_mix_calls")
+        print(json.dumps({"mix": {"decode_calls": calls[0], "prefill_calls": calls[1], "nan_rows_not_zero": calls[2],
+                                  "decode_max_abs_diff": mx[0], "prefill_max_abs_diff": mx[1], "decode_max_abs_ref": mx[2],
+                                  "prefill_max_abs_ref": mx[3]}}))
     toks = cfg["batch"] * cfg["max_gen_len"]
     push = push_used if (args.variant == "tp" and world > 1) else False
     print(json.dumps({"variant": args.variant, "tp": world, "tp_decode_exchange": ("peer stores" if push else ("nccl" if world > 1 else None)),

@@ -22,6 +22,17 @@ static flb_tp_ctx g_tp; // this rank's communicator block: owned by the program,
 
 extern "C" {
 
+// Test hooks read by the patched generation loop (make_e2e_variants.py: patch_probe) and by the `mix` variant's
+// side-by-side comparison (patch_mix).  NULL / zero: no effect.
+float *flb_e2e_logits_out = nullptr;       // device [steps, batch, vocab]: every step's logits row, as the sampler read it
+const int *flb_e2e_forced_ids = nullptr;   // device [steps, batch]: ids that replace the sampled ones (teacher forcing)
+double flb_e2e_mix_max[4] = {0, 0, 0, 0};  // max |ref - flb| over decode / prefill calls, max |ref| over decode / prefill
+long flb_e2e_mix_calls[3] = {0, 0, 0};     // decode calls compared, prefill calls compared, rows the reference left NaN and ours not 0
+void e2e_set_probe(float *logits_out, const int *forced_ids) {
+    flb_e2e_logits_out = logits_out;
+    flb_e2e_forced_ids = forced_ids;
+}
+
 typedef struct e2e_layer {
     void *attn_gamma;
     int8_t *wq, *wk, *wv, *wo;

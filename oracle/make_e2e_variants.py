@@ -10,6 +10,8 @@ reference is committed here; the copy lives under oracle/_ref/, which is git-ign
         (the whole attention section) replaced by one call of flb_open_decoder_attention()
         (include/flb_open_decoder.h) — the drop-in adaptor.
 
+  oracle/_ref/libe2e_opt.so   libe2e_flb.so plus the steps either side of the attention call (patch_opt): one merged QKV GEMM
+        read in place, the LM head over the last rows only, an asynchronous finished check, an fp16-sized cache slab.
   oracle/_ref/libe2e_tp.so    the tensor-parallel layer: like libe2e_flb.so, plus the Q/K/V GEMMs restricted to the rank's
         column slice of the weights and flb_open_decoder_attention_tp() (head-sharded attention + one NCCL all-gather).
   oracle/_ref/libe2e_ref32.so like libe2e_ref.so, but with the prefill GEMMs computing in true fp32
@@ -72,6 +74,26 @@ def patch_gemv(src: str) -> None:
     open(p, "w").write(t)
 
 
+def patch_probe(src: str) -> None:
+    """Test hooks in the generation loop (every variant): when the runner has set them, each step's logits row
+    [batch, vocab] (what the sampling kernels read) is copied out, and the sampled ids are overwritten with forced ones
+    (teacher forcing with another run's ids).  Both pointers live in e2e_runner.cu and are NULL by default."""
+    p = os.path.join(src, "cuda", "decoding_sampling.cu")
+    t = open(p).read()
+    t = _sub(t, r'(#include "decoding_sampling.h"\n)', r'\1extern "C" {\nextern float *flb_e2e_logits_out;\nextern const int *flb_e2e_forced_ids;\n}\n', 1, "probe externs")
+    t = _sub(t, r"(launchUpdateLogitsWithoutSoftmax\(step_logits_buf_, logits_buf_, args_\.end_id_, finished_buf_, args_\.batch_size_,[^;]*;)",
+             r"""\1
+                if (flb_e2e_logits_out)
+                    cudaMemcpyAsync(flb_e2e_logits_out + (size_t)(step - 1) * args_.batch_size_ * args_.vocab_size_, step_logits_buf_,
+                                    sizeof(float) * args_.batch_size_ * args_.vocab_size_, cudaMemcpyDeviceToDevice, decoding_params.stream);""", 1, "logits probe")
+    t = _sub(t, r"(launchTopKSamplingKernel\(step_logits_buf_, topk_ids_buf_, topk_val_buf_,[^;]*;)",
+             r"""\1
+                if (flb_e2e_forced_ids)
+                    cudaMemcpyAsync(word_ids_buf_ + (step - 1) * args_.batch_size_, flb_e2e_forced_ids + (size_t)(step - 1) * args_.batch_size_,
+                                    sizeof(int) * args_.batch_size_, cudaMemcpyDeviceToDevice, decoding_params.stream);""", 1, "forced ids")
+    open(p, "w").write(t)
+
+
 def patch_ctx(src: str) -> None:
     """The binding's per-object state: a flb_open_decoder_ctx member of OpenDecoder, initialised in its constructor."""
     p = os.path.join(src, "open_decoder.h")
@@ -82,6 +104,69 @@ def patch_ctx(src: str) -> None:
     p = os.path.join(src, "cuda", "open_decoder.cu")
     t = open(p).read()
     t = _sub(t, r"(\n        hidden_units_ = head_num_ \* size_per_head_;\n)", r"\1        flb_open_decoder_ctx_init(&flb_ctx_);\n", 1, "ctx init")
+    open(p, "w").write(t)
+
+
+def patch_opt(src: str) -> None:
+    """On top of the adaptor: the rows of the scope table that lie either side of the attention call.
+    (1) One INT8 GEMM for the Q, K and V projections when the binding has a packed weight matrix (FLB_MERGED_QKV=1);
+        q, k and v are then column blocks of one buffer and reach the attention call with their row stride.
+    (2) The LM head over the last row of each sequence only: nothing else is ever read from the logits
+        (decoding_kernels.cu:255-275 takes row seq_len - 1), the reference computes all batch x prompt rows.
+    (3) The "is everybody finished" copy of every step made asynchronous and looked at one step later: the loop may run
+        one step longer, which cannot change an output (a finished sequence keeps its length and emits end_id).
+    (4) With FLB_CACHE_F16=1 the cache slab is allocated at the size fp16 needs."""
+    p = os.path.join(src, "cuda", "open_decoder.cu")
+    t = open(p).read()
+    t = _sub(t, r"(int k = hidden_units_;\n)(\s*)(CHECK_CUBLAS_STATUS\(cublasGemmEx\(param_\.cublas_handle,)",
+             r"""\1\2const int8_t *flb_wqkv = flb_open_decoder_packed_qkv(&flb_ctx_, (const int8_t *)param_.attention.query_weight.kernel,
+\2        (const int8_t *)param_.attention.key_weight.kernel, (const int8_t *)param_.attention.value_weight.kernel, n, param_.stream);
+\2if (flb_wqkv) {
+\2CHECK_CUBLAS_STATUS(cublasGemmEx(param_.cublas_handle, CUBLAS_OP_N, CUBLAS_OP_N, 3 * n, m, k, &weight_alpha,
+\2        (const weight_DataType_ *)flb_wqkv, weight_Traits_::AType, 3 * n, from_tensor_int8_buf_, weight_Traits_::BType, k, &weight_beta,
+\2        query_buf_, weight_Traits_::CType, 3 * n, weight_Traits_::computeType, static_cast<cublasGemmAlgo_t>(cublasAlgo_[0])));
+\2} else {
+\2\3""", 1, "merged QKV GEMM")
+    t = _sub(t, r"(\n\s*)(flb_open_decoder_attention\(&flb_ctx_, batch_size_, head_num_, size_per_head_, max_prompt_len_, total_len_, seq_len, start_pos,\n\s*)query_buf_, key_buf_, value_buf_, hidden_units_,",
+             r"\1}\1\2query_buf_, flb_wqkv ? query_buf_ + n : key_buf_, flb_wqkv ? query_buf_ + 2 * n : value_buf_, flb_wqkv ? 3 * n : n,", 1, "strided q/k/v")
+    t = _sub(t, r"(OpenDecoder<OpType_, QuantizationType>::~OpenDecoder\(\)\n\s*\{\n)", r"\1        flb_open_decoder_ctx_destroy(&flb_ctx_);\n", 1, "ctx destroy")
+    open(p, "w").write(t)
+
+    p = os.path.join(src, "cuda", "decoding_sampling.cu")
+    t = open(p).read()
+    # (2) LM head on the last rows: B columns of k elements, cur_seq_len * k apart
+    t = _sub(t, r"int m = args_\.batch_size_ \* cur_seq_len;", "int m = args_.batch_size_;", 1, "lm head rows")
+    t = _sub(t, r"decoder_normed_result_buf_, BType_, k,", "decoder_normed_result_buf_ + (size_t)(cur_seq_len - 1) * k, BType_, k * cur_seq_len,", 1, "lm head operand")
+    t = _sub(t, r"(launchUpdateLogitsWithoutSoftmax\(step_logits_buf_, logits_buf_, args_\.end_id_, finished_buf_, args_\.batch_size_,\s*)cur_seq_len,", r"\g<1>1,", 1, "top-k logits row")
+    t = _sub(t, r"(launchUpdateLogitsKernelWithoutLog\(step_logits_buf_, logits_buf_, finished_buf_, )cur_seq_len,", r"\g<1>1,", 1, "top-p logits row")
+    # (3) lagged, asynchronous finished check
+    t = _sub(t, r"(\n\s*)int prev_pos = 0;\n", r"""\1int prev_pos = 0;
+\1bool *flb_fin_host = nullptr;
+\1cudaEvent_t flb_fin_event;
+\1bool flb_fin_pending = false;
+\1CHECK_CUDA_ERROR(cudaHostAlloc((void **)&flb_fin_host, sizeof(bool) * args_.batch_size_, cudaHostAllocDefault));
+\1CHECK_CUDA_ERROR(cudaEventCreateWithFlags(&flb_fin_event, cudaEventDisableTiming));
+""", 1, "finished-check set-up")
+    t = _sub(t, r"cudaMemcpy\(h_finished_buf_, finished_buf_, sizeof\(bool\) \* args_\.batch_size_, cudaMemcpyDeviceToHost\);\n(\s*)int sum = 0;\n\s*for \(int i = 0; i < args_\.batch_size_; i\+\+\)\n\s*\{\n\s*sum \+= h_finished_buf_\[i\] \? 1 : 0;\n\s*\}",
+             r"""int sum = 0;
+\1if (flb_fin_pending && cudaEventQuery(flb_fin_event) == cudaSuccess)
+\1{
+\1    for (int i = 0; i < args_.batch_size_; i++) sum += flb_fin_host[i] ? 1 : 0;
+\1    flb_fin_pending = false;
+\1}
+\1if (!flb_fin_pending && sum != args_.batch_size_)
+\1{
+\1    cudaMemcpyAsync(flb_fin_host, finished_buf_, sizeof(bool) * args_.batch_size_, cudaMemcpyDeviceToHost, decoding_params.stream);
+\1    cudaEventRecord(flb_fin_event, decoding_params.stream);
+\1    flb_fin_pending = true;
+\1}""", 1, "finished check")
+    t = _sub(t, r"(\n\s*)(launchRemovePromptTokenKernel\(decoding_params\.output_ids,)", r"""\1cudaStreamSynchronize(decoding_params.stream);
+\1cudaEventDestroy(flb_fin_event);
+\1cudaFreeHost(flb_fin_host);
+\1\2""", 1, "finished-check tear-down")
+    # (4) fp16 cache slab
+    t = _sub(t, r"(size_t cache_size = args_\.batch_size_ \* \(args_\.max_prompt_len_ \+ args_\.max_gen_len_\) \* args_\.hidden_units_;)",
+             'size_t cache_size = (size_t)args_.batch_size_ * (args_.max_prompt_len_ + args_.max_gen_len_) * args_.hidden_units_ / (flb_open_decoder_env_int("FLB_CACHE_F16", 0) ? 2 : 1);', 2, "fp16 slab")
     open(p, "w").write(t)
 
 
@@ -123,9 +208,11 @@ def patch_mix(src: str) -> None:
                                        key_cache_, value_cache_, query_out_buf_, qk_buf_, qkv_buf_, from_tensor_int8_buf_, from_tensor_scale_buf_, param_.stream);
             } else {"""
     tail = """            }
-            if ((flb_use & 4) && seq_len == 1) {
-                // diagnostic: run the adaptor on the same inputs after the reference section and report the difference
-                static int ncmp = 0;
+            if (flb_use & 4) {
+                // diagnostic: run the adaptor on the same inputs after the reference section and record the difference
+                // (every decode call and every prefill call; the reference's result is kept, so the run stays on the
+                // reference's own trajectory: teacher forcing at the level of one attention call)
+                const int ph = seq_len > 1 ? 1 : 0;
                 const size_t n = (size_t)batch_size_ * head_num_ * seq_len * size_per_head_;
                 std::vector<float> h_ref(n), h_flb(n);
                 cudaStreamSynchronize(param_.stream);
@@ -138,14 +225,20 @@ def patch_mix(src: str) -> None:
                 cudaStreamSynchronize(param_.stream);
                 cudaMemcpy(h_flb.data(), qkv_buf_, n * sizeof(float), cudaMemcpyDeviceToHost);
                 cudaMemcpy(qkv_buf_, h_ref.data(), n * sizeof(float), cudaMemcpyHostToDevice);
-                double mx = 0, amax = 0; size_t at = 0;
-                for (size_t i = 0; i < n; ++i) { double d = fabs((double)h_ref[i] - h_flb[i]); if (d > mx) { mx = d; at = i; } amax = fmax(amax, fabs((double)h_ref[i])); }
-                if (ncmp < 70) printf("[cmp %d] start_pos %d max|ref-flb| %.3e at %zu (ref %.6f flb %.6f) max|ref| %.3f\\n", ncmp, start_pos, mx, at, h_ref[at], h_flb[at], amax);
-                ++ncmp;
+                double mx = 0, amax = 0; size_t at = 0, bad = 0;
+                for (size_t i = 0; i < n; ++i) {
+                    if (std::isnan(h_ref[i])) { if (h_flb[i] != 0.0f) ++bad; continue; } // the reference's 0/0 on a fully masked row: ours is 0
+                    double d = fabs((double)h_ref[i] - h_flb[i]); if (d > mx) { mx = d; at = i; } amax = fmax(amax, fabs((double)h_ref[i]));
+                }
+                flb_e2e_mix_calls[ph] += 1;
+                flb_e2e_mix_max[ph] = fmax(flb_e2e_mix_max[ph], mx);
+                flb_e2e_mix_max[2 + ph] = fmax(flb_e2e_mix_max[2 + ph], amax);
+                flb_e2e_mix_calls[2] += (long)bad;
+                if (flb_e2e_mix_calls[ph] <= 8) printf("[cmp %s %ld] start_pos %d seq_len %d max|ref-flb| %.3e at %zu (ref %.6f flb %.6f) max|ref| %.3f\\n", ph ? "prefill" : "decode", flb_e2e_mix_calls[ph], start_pos, seq_len, mx, at, h_ref[at], h_flb[at], amax);
             }"""
     lines[s:e] = head.split("\n") + lines[s:e] + tail.split("\n")
     text = "\n".join(lines)
-    text = text.replace('#include "open_decoder.h"', '#include <vector>\n#include <cmath>\n#include "open_decoder.h"', 1)
+    text = text.replace('#include "open_decoder.h"', '#include <vector>\n#include <cmath>\n#include "open_decoder.h"\nextern "C" {\nextern double flb_e2e_mix_max[4];\nextern long flb_e2e_mix_calls[3];\n}', 1)
     open(p, "w").write(text)
 
 
@@ -191,6 +284,7 @@ def build(name: str, ref_root: str) -> str:
         for x in ds + fs:
             os.chmod(os.path.join(r, x), 0o755 if x in ds else 0o644)
     patch_sizes(src)
+    patch_probe(src)
     if name in ("ref", "ref32"):
         patch_gemv(src)
     elif name == "mix":
@@ -199,8 +293,10 @@ def build(name: str, ref_root: str) -> str:
         patch_tp(src)
     else:
         patch_adaptor(src)
-    if name in ("flb", "mix", "tp"):
+    if name in ("flb", "mix", "tp", "opt"):
         patch_ctx(src)  # after the section patches: those address open_decoder.cu by line number
+    if name == "opt":
+        patch_opt(src)
     if name == "ref32":
         p = os.path.join(src, "cuda", "common.h")
         t = open(p).read()
@@ -211,7 +307,7 @@ def build(name: str, ref_root: str) -> str:
     cmd = ["nvcc", "-std=c++17", "-O3", "-DNDEBUG", "-w", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
            "-shared", "-cudart", "shared", "-I", src, "-I", os.path.join(src, "cuda"), "-I", os.path.join(ROOT, "include"),
            *cu, os.path.join(HERE, "e2e_runner.cu"), "-lcublas", "-lcurand", "-o", lib]
-    if name in ("flb", "mix", "tp"):
+    if name in ("flb", "mix", "tp", "opt"):
         pkg = os.path.join(ROOT, "fasterllama_b200")
         cmd += ["-L", pkg, "-lflb_attn", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../fasterllama_b200"]
     if name == "mix":
@@ -231,7 +327,7 @@ def main(ref_root: str | None = None) -> None:
     if not ref_root or not os.path.isdir(os.path.join(ref_root, "fasterLlama")):
         raise SystemExit("usage: make_e2e_variants.py <reference checkout> [variants...]  (or set FLB_REFERENCE_ROOT)")
     os.makedirs(OUT, exist_ok=True)
-    for name in (sys.argv[2:] or ["ref", "flb", "ref32", "mix", "tp"]):
+    for name in (sys.argv[2:] or ["ref", "flb", "ref32", "mix", "tp", "opt"]):
         print("built", build(name, ref_root))
 
 

@@ -221,6 +221,43 @@ def test_early_start_calls_back_to_back(cuda_device):
             assert torch.equal(a, b)
 
 
+def test_early_start_level1_behind_a_slow_writer(cuda_device):
+    """Level 1 promises only that the cached rows are settled; q, k and v may still be on their way.  Here they are
+    produced by a copy that sits behind a slow matrix product, TWO launches in front of the call under test, with
+    another early-started decode call between them (a kernel that lets its successor start before it has finished
+    itself).  The call must still see the finished inputs: it reads them only after the kernel in front has
+    completed, and that kernel completes only after everything in front of it."""
+    import torch
+
+    from fasterllama_b200 import workloads as W2
+
+    lens = W2.draw_lengths(9, 4, 100, 900)
+    mk = lambda seed: W2.device_case("slow-writer", seed, 4, 8, 901, lens, device=cuda_device)  # noqa: E731
+    ref = mk(71)
+    A.decode(ref.params())
+    torch.cuda.synchronize()
+    want = ref.arrays["out"].clone()
+
+    between, late = mk(72), mk(71)  # `late` has the reference's caches; its q, k, v arrive late
+    final = {n: late.arrays[n].clone() for n in ("q", "k", "v")}
+    for n in ("q", "k", "v"):
+        late.arrays[n].zero_()
+    for c in (between, late):
+        c.scratch_zeroed = True
+        c.early_start = 1
+    big = torch.randn((6144, 6144), device=cuda_device)
+    p_between, p_late = between.params(), late.params()
+    torch.cuda.synchronize()
+    torch.mm(big, big)                       # milliseconds of work in front of the writer
+    for n in ("q", "k", "v"):
+        late.arrays[n].copy_(final[n])       # the writer of the late call's inputs
+    A.decode(p_between)                      # early-started, unrelated buffers
+    A.decode(p_late)                         # early-started: may be resident long before its inputs exist
+    torch.cuda.synchronize()
+    assert A.scratch_status(late.arrays["scratch"]) == 0 and A.scratch_status(between.arrays["scratch"]) == 0
+    assert torch.equal(late.arrays["out"], want)
+
+
 def test_config4_fp16_13b_full_size_properties(cuda_device):
     """fp16, batch 64, 40 heads x 128, lengths uniform in [2048, 4096], seed 3 — full size (5.4 GB of cache drawn
     on the GPU).  The oracle checks a sample of (batch, head) units; size-independent properties cover the rest:

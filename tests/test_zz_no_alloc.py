@@ -56,6 +56,35 @@ def test_static_scratch_matches_regular_entry_point_twice(cuda_device):
     assert np.array_equal(gk, wk)
 
 
+@pytest.mark.gpu
+def test_static_scratch_status_reports_a_bad_length(cuda_device):
+    """The kernels' error word lives inside the library's block, out of the caller's reach: the accessor reads it.
+    A cached length beyond the slab (a caller bug) is clamped by the kernel and reported as bit 4; the next
+    well-formed call through the same entry point starts from a clean word again."""
+    import torch
+
+    assert A.static_scratch_status() in (0, 4)  # whatever an earlier test left; never a wait that ran out
+    lens = np.array([100, 50], dtype=np.int32)
+    case = W.host_case("noalloc-bad", 43, 2, 4, 256, past=lens)
+    case.max_past_len = 255
+    dev = W.to_device(case, cuda_device)
+    dev.pop("scratch")
+    good = case.params(dev)
+    A.decode_static_scratch(good)
+    torch.cuda.synchronize()
+    assert A.static_scratch_status() == 0
+    want = dev["out"].float().cpu().numpy().copy()
+    dev["past_lens"] = torch.tensor([100, 100000], dtype=torch.int32, device=cuda_device)  # second entry is nonsense
+    A.decode_static_scratch(case.params(dev))
+    torch.cuda.synchronize()
+    assert A.static_scratch_status() & 4, "the clamped length was not reported"
+    dev["past_lens"] = torch.from_numpy(lens).to(cuda_device)
+    A.decode_static_scratch(case.params(dev))
+    torch.cuda.synchronize()
+    assert A.static_scratch_status() == 0
+    assert np.array_equal(dev["out"].float().cpu().numpy()[0], want[0])  # the sequence with a valid length
+
+
 def test_static_scratch_refuses_what_does_not_fit():
     """Host-side check only: a batch whose partitions overflow the fixed block is refused with
     FLB_ERR_TOO_LARGE before any CUDA call."""
