@@ -543,6 +543,30 @@ def leg_exchange(rank, world, local, stream) -> dict:
     for name, fn in (("decode_only_us", step_none), ("decode_nccl_all_gather_us", step_nccl), ("decode_peer_stores_exchange_us", step_push)):
         _, t, _ = timed(fn, 200, 20, world, stream)
         res[name] = round(t / 200 * 1e6, 2)
+    # The prefill gather of the same layer (batch 32 x 512 tokens): what the binding does today — an all-gather of the fp32
+    # head outputs, 256 MiB per layer — against the exchange that moves a quarter of the bytes and is bit-exact too:
+    # all-reduce(max) of the per-token absmax, quantise locally, all-gather the int8 rows.  Collectives only: this sizes
+    # what a change of the prefill exchange could save, it is not a second code path.
+    S = 512
+    shard = torch.empty((B * S * hl * 128,), dtype=torch.float32, device=dev)
+    full32 = torch.empty((world, shard.numel()), dtype=torch.float32, device=dev)
+    amax = torch.rand((B * S,), device=dev)
+    shard8 = torch.empty((shard.numel(),), dtype=torch.int8, device=dev)
+    full8 = torch.empty((world, shard.numel()), dtype=torch.int8, device=dev)
+
+    def gather32(i):
+        dist.all_gather_into_tensor(full32, shard)
+
+    def gather8(i):
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX)
+        dist.all_gather_into_tensor(full8, shard8)
+
+    _, t32, _ = timed(gather32, 20, 3, world, stream)
+    _, t8, _ = timed(gather8, 20, 3, world, stream)
+    res["prefill_gather"] = {"tokens": B * S, "fp32_all_gather_us": round(t32 / 20 * 1e6, 1), "fp32_bytes_per_rank": shard.numel() * 4 * world,
+                             "absmax_all_reduce_plus_int8_all_gather_us": round(t8 / 20 * 1e6, 1), "int8_bytes_per_rank": shard.numel() * world,
+                             "what": "NCCL collectives alone, per layer, at the end-to-end configuration's prefill (32 x 512 tokens)"}
+    del shard, full32, shard8, full8
     res["exchange_status"] = int(A.scratch_status(loc["scratch"]))
     # what the push delivered is what the all-gather delivered
     step_nccl(0)
