@@ -57,6 +57,13 @@ def build_oracle(force: bool = False) -> str:
     return ORACLE_LIB
 
 
+def reference_root() -> str | None:
+    """Where the reference checkout lies on this machine: FLB_REFERENCE_ROOT, else a directory named `reference`
+    beside this repository.  None when neither exists (the prebuilt files under oracle/_ref are then used as they are)."""
+    cand = os.environ.get("FLB_REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "fasterLlama", "cuda")) else None
+
+
 def build_reference(force: bool = False) -> str | None:
     """Compiles the reference's own CUDA kernels (from the read-only reference checkout, where
     present) plus the runner in oracle/ref_runner.cu into oracle/_ref/.  Returns None when the
@@ -65,8 +72,8 @@ def build_reference(force: bool = False) -> str | None:
     if not os.path.exists(script):
         return None
     out = os.path.join(ORACLE_DIR, "_ref", "libflb_ref.so")
-    ref_root = os.environ.get("FLB_REFERENCE_ROOT", "/root/reference")
-    if not os.path.isdir(ref_root):
+    ref_root = reference_root()
+    if ref_root is None:
         return out if os.path.exists(out) else None
     if not force and os.path.exists(out) and os.path.getmtime(out) >= os.path.getmtime(os.path.join(ORACLE_DIR, "ref_runner.cu")):
         return out
@@ -81,10 +88,10 @@ def build_e2e_variants(force: bool = False) -> list[str]:
     """End-to-end libraries around the reference's own DecodingSampling/OpenDecoder classes (test and baseline
     infrastructure, oracle/make_e2e_variants.py).  Built only where the reference checkout exists; stale ones are
     rebuilt when the runner, the patch script or the binding headers changed."""
-    ref_root = os.environ.get("FLB_REFERENCE_ROOT", "/root/reference")
+    ref_root = reference_root()
     out_dir = os.path.join(ORACLE_DIR, "_ref")
     libs = [os.path.join(out_dir, f"libe2e_{v}.so") for v in E2E_VARIANTS]
-    if not os.path.isdir(ref_root):
+    if ref_root is None:
         return [l for l in libs if os.path.exists(l)]
     deps = [os.path.join(ORACLE_DIR, "e2e_runner.cu"), os.path.join(ORACLE_DIR, "make_e2e_variants.py"),
             os.path.join(ROOT, "include", "flb_open_decoder.h"), os.path.join(ROOT, "include", "flb_attn.h")]

@@ -18,6 +18,15 @@ enum : unsigned {
     kErrConsumerWait = 2u,  // a compute warp gave up waiting for a stage to land
 };
 
+// SMs of the current device (0 when the query fails).  Grid sizes that must stay co-resident, or that are sized in
+// waves, are computed from this and not from a constant.
+inline int current_device_sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return sms;
+}
+
 struct DecodeArgs {
     int B, H, T;
     int start_pos;

@@ -286,7 +286,10 @@ extern "C" int flb_attn_classify_mask(const float *attn_mask, int rows, int row_
     const unsigned all = 7u;
     if (cudaMemcpyAsync(maskbits, &all, sizeof(all), cudaMemcpyHostToDevice, stream) != cudaSuccess) return FLB_ERR_LAUNCH;
     const size_t n = (size_t)rows * rows;
-    const unsigned blocks = (unsigned)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+    const int sms = flb::current_device_sm_count();
+    if (sms <= 0) return FLB_ERR_DEVICE;
+    const size_t cap = (size_t)sms * 8; // a grid-stride loop: eight blocks of 256 threads per SM fill the machine
+    const unsigned blocks = (unsigned)((n + 255) / 256 < cap ? (n + 255) / 256 : cap);
     classify_mask_kernel<<<blocks, 256, 0, stream>>>(attn_mask, rows, row_stride, maskbits);
     if (cudaGetLastError() != cudaSuccess) return FLB_ERR_LAUNCH;
     unsigned v = 0;

@@ -19,6 +19,7 @@
 // before it waits, so the ranks cannot dead-lock each other however their kernels are scheduled.
 // Flag words only grow; comparison is by signed difference, so the 32-bit epoch may wrap.
 #include "../../include/flb_attn.h"
+#include "decode_attn.cuh"
 
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -161,7 +162,9 @@ extern "C" int flb_attn_peer_exchange(const flb_peer_exchange *x, void *cuda_str
     size_t blocks = copy ? (a.n_vec + 256 * 4 - 1) / (256 * 4) : 1;
     if (quant && blocks < (size_t)x->q8_rows) blocks = (size_t)x->q8_rows;
     if (blocks < 1) blocks = 1;
-    if (blocks > 148) blocks = 148;
+    const int sms = flb::current_device_sm_count();
+    if (sms <= 0) return FLB_ERR_DEVICE;
+    if (blocks > (size_t)sms) blocks = (size_t)sms;
     flb_peer_exchange_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(a);
     return cudaGetLastError() == cudaSuccess ? FLB_OK : FLB_ERR_LAUNCH;
 }

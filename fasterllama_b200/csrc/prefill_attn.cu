@@ -41,6 +41,8 @@
 //    head-split layer on several GPUs.
 #include "prefill_attn.cuh"
 
+#include "decode_attn.cuh"
+
 #include "flb_ptx.cuh"
 
 #include <cuda_fp16.h>
@@ -910,9 +912,8 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
         ok = ok && make_map(enc, &tmK, a.kh, B * H, S, S, BN) && make_map(enc, &tmV, a.vh, B * H, S, S, BN);
     }
     if (!ok) return FLB_ERR_LAUNCH;
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-        return FLB_ERR_DEVICE;
+    const int sms = current_device_sm_count();
+    if (sms <= 0) return FLB_ERR_DEVICE;
 
     cudaLaunchConfig_t cfg = {};
     cfg.stream = stream;

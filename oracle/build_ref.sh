@@ -3,9 +3,9 @@
 # reference checkout where it lies — nothing is copied into this repository) plus the runner in
 # ref_runner.cu, for sm_100a.  The reference's CMake build is not used (it pins sm_75 and a
 # CUDA 11.7 path); its two kernel translation units compile as they are with nvcc 12.9.
-# usage: build_ref.sh [reference-root]
+# usage: build_ref.sh <reference-root>
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:?usage: build_ref.sh <reference-root>}"
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 OUT="$HERE/_ref"
 mkdir -p "$OUT"
