@@ -155,11 +155,12 @@ def make_params(
     return p
 
 
-def workspace_bytes(batch_size: int, head_num: int, total_len: int, seq_len: int = 1, split_len: int = 0) -> int:
+def workspace_bytes(batch_size: int, head_num: int, total_len: int, seq_len: int = 1, split_len: int = 0,
+                    size_per_head: int = 128) -> int:
     """Scratch bytes for every call these dimensions allow (decode on a full cache, prefill of
     `seq_len` tokens)."""
     p = FlbAttnParams()
-    p.batch_size, p.head_num, p.size_per_head = batch_size, head_num, 128
+    p.batch_size, p.head_num, p.size_per_head = batch_size, head_num, size_per_head
     p.total_len, p.seq_len, p.split_len = total_len, seq_len, split_len
     n = C.c_size_t(0)
     _lib.check(_lib.load_library().flb_attn_workspace_bytes(C.byref(p), C.byref(n)))

@@ -67,12 +67,13 @@ template <> struct CacheIO<__half> {
 // One element of q/k/v for sequence b, head h, dim i with seq_len == 1: [B,1,H,d] with row_stride elements
 // between sequences (H*d when dense).
 // FLB_IN_INT32: float(acc) * act_scale[b] * w_scale[h*d+i], in this order (decoder_kernels.cu:449).
+template <int D>
 __device__ __forceinline__ float load_input(const DecodeArgs &a, const void *base, const float *w_scale, int unit, int b,
                                             int h, int i) {
-    const size_t off = (size_t)b * a.row_stride + (size_t)h * kHeadDim + i;
+    const size_t off = (size_t)b * a.row_stride + (size_t)h * D + i;
     if (a.input_mode == 0) {
         const float acc = (float)__ldg((const int32_t *)base + off);
-        return acc * __ldg(a.act_scale + b) * __ldg(w_scale + (size_t)h * kHeadDim + i);
+        return acc * __ldg(a.act_scale + b) * __ldg(w_scale + (size_t)h * D + i);
     } else if (a.input_mode == 1) {
         return __ldg((const float *)base + off);
     }
@@ -84,8 +85,7 @@ __device__ __forceinline__ float load_input(const DecodeArgs &a, const void *bas
 // One element of a finished output row: into `out` [B, H, d], or — head-split layer — into every rank's
 // [B, out_head_total, d] buffer (plain stores; the remote ones travel over NVLink and are published by the
 // exchange kernel that follows on the stream).
-__device__ __forceinline__ void store_out_element(const DecodeArgs &a, int unit, int col, float r) {
-    constexpr int D = kHeadDim;
+template <int D> __device__ __forceinline__ void store_out_element(const DecodeArgs &a, int unit, int col, float r) {
     if (a.n_out_peers == 0) {
         const size_t oo = (size_t)unit * D + col;
         if (a.out_f16)
@@ -109,9 +109,9 @@ __device__ __forceinline__ void store_out_element(const DecodeArgs &a, int unit,
 // for its sequence (an arrival counter per sequence; nobody waits) reads the whole [H, d] fp32 row back,
 // takes absmax over all heads with the reference's -1e9f floor, writes absmax / 127 and the codes
 // cvt.rni.sat.s8(x * 127.0f / absmax) as [H*d].  All threads of the CTA must call it.
-template <int NWARPS>
+template <int D, int NWARPS>
 __device__ __forceinline__ void quantize_row_if_last(const DecodeArgs &a, int b, float *red, int *flag) {
-    constexpr int D = kHeadDim;
+    constexpr int NC = NWARPS * 32; // threads that take part in the row pass: thread t owns dims t, t + NC, ...
     const int tid = threadIdx.x;
     __syncthreads(); // the head's output stores precede the fence of thread 0
     if (tid == 0) {
@@ -124,43 +124,48 @@ __device__ __forceinline__ void quantize_row_if_last(const DecodeArgs &a, int b,
     __threadfence();
     const float *row = (const float *)a.out + (size_t)b * a.H * D;
     float amax = -1e9f;
-    if (tid < D)
-        for (int h = 0; h < a.H; ++h) amax = fmaxf(amax, fabsf(__ldcg(row + (size_t)h * D + tid)));
+    if (tid < NC)
+        for (int i = tid; i < D; i += NC)
+            for (int h = 0; h < a.H; ++h) amax = fmaxf(amax, fabsf(__ldcg(row + (size_t)h * D + i)));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    if (tid < D && (tid & 31) == 0) red[tid >> 5] = amax;
+    if (tid < NC && (tid & 31) == 0) red[tid >> 5] = amax;
     __syncthreads();
     amax = red[0];
 #pragma unroll
-    for (int w = 1; w < D / 32; ++w) amax = fmaxf(amax, red[w]);
+    for (int w = 1; w < NWARPS; ++w) amax = fmaxf(amax, red[w]);
     if (tid == 0) {
         a.out_q8_scale[b] = amax / 127.0f;
         a.row_counters[b] = 0u; // ready for the next call
     }
-    if (tid < D) {
+    if (tid < NC) {
         int8_t *dst = a.out_q8 + (size_t)b * a.H * D;
-        for (int h = 0; h < a.H; ++h) {
-            const float x = __ldcg(row + (size_t)h * D + tid) * 127.0f / amax;
-            int q;
-            asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(x));
-            dst[(size_t)h * D + tid] = (int8_t)q;
-        }
+        for (int i = tid; i < D; i += NC)
+            for (int h = 0; h < a.H; ++h) {
+                const float x = __ldcg(row + (size_t)h * D + i) * 127.0f / amax;
+                int q;
+                asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(x));
+                dst[(size_t)h * D + i] = (int8_t)q;
+            }
     }
 }
 
-template <typename CacheT, int TILE_ROWS, int STAGES, int NWARPS>
+template <typename CacheT, int HD, int TILE_ROWS, int STAGES, int NWARPS>
 __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(const __grid_constant__ DecodeArgs a) {
-    constexpr int D = kHeadDim;
+    constexpr int D = HD;
     constexpr int ROW_BYTES = D * (int)sizeof(CacheT);
-    constexpr int EPL = 16 / (int)sizeof(CacheT); // elements per lane (one 16-byte chunk)
-    constexpr int LPR = D / EPL;                  // lanes per cache row
+    constexpr int EPL = 16 / (int)sizeof(CacheT); // elements per 16-byte chunk
+    constexpr int CHUNKS = D / EPL;               // chunks per cache row
+    constexpr int LPR = CHUNKS < 32 ? CHUNKS : 32; // lanes per cache row
+    constexpr int CPL = CHUNKS / LPR;             // chunks per lane: lane c owns chunks c, c + LPR, ...
     constexpr int RPI = 32 / LPR;                 // rows a warp takes per step
     constexpr int ITERS = TILE_ROWS / (NWARPS * RPI);
     constexpr int TILE_BYTES = TILE_ROWS * ROW_BYTES;
-    constexpr int NC = NWARPS * 32; // compute threads
+    constexpr int NC = NWARPS * 32;               // compute threads
+    constexpr int DPT = (D + NC - 1) / NC;        // head dimensions per compute thread: t, t + NC, ...
     static_assert(ITERS * NWARPS * RPI == TILE_ROWS, "tile rows must divide over the compute warps");
-    static_assert(NC >= D, "need one compute thread per head dimension");
-    static_assert(LPR == 16 || LPR == 32, "row must span 16 or 32 lanes");
+    static_assert(LPR * CPL * EPL == D && LPR * RPI == 32, "a row must map onto whole lanes");
+    static_assert((NC % 2) == 0, "RoPE pairs sit in neighbouring lanes");
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + (size_t)STAGES * 2 * TILE_BYTES);
@@ -204,7 +209,9 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
     }
     __syncthreads();
 
-    float vnew = 0.0f;   // thread t < D of the last partition: new v[t], rounded to the cache type
+    float vnew[DPT];     // compute thread t of the last partition: new v[t + NC e], rounded to the cache type
+#pragma unroll
+    for (int e = 0; e < DPT; ++e) vnew[e] = 0.0f;
     float s_new = 0.0f;  // score of the new key in the log2 domain
     bool new_visible = false;
 
@@ -241,40 +248,45 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
         // streaming pass over the cache runs first and only the new token's v, the cache append and the
         // result/scratch writes wait (after the loop below).
         if (a.early_start == 1) grid_dependency_wait();
-        float krot_keep = 0.f; // the new token's rotated k, appended to the cache after the streaming pass
+        float krot_keep[DPT]; // the new token's rotated k, appended to the cache after the streaming pass
         // -- the new token: dequantise, rotate (a2 of the reference); its v and the append (a3, a4) follow the loop
         {
-            float qraw = 0.f, kraw = 0.f;
-            if (tid < D) {
-                qraw = load_input(a, a.q, a.q_w_scale, unit, b, h, tid);
-                if (is_last) kraw = load_input(a, a.k, a.k_w_scale, unit, b, h, tid);
-            }
-            float qrot = qraw, krot = kraw;
-            if (a.freq_cis) {
-                // pairs (2i, 2i+1) sit in neighbouring lanes of one warp
-                const float qo = __shfl_xor_sync(0xffffffffu, qraw, 1);
-                const float ko = __shfl_xor_sync(0xffffffffu, kraw, 1);
-                if (tid < D) {
-                    const int row = a.rope_pos0 + (a.rope_add_past ? past : 0);
-                    const float *fr = a.freq_cis + (size_t)row * D;
-                    const float c = __ldg(fr + (tid & ~1)), sn = __ldg(fr + (tid | 1));
-                    if (tid & 1) {
-                        qrot = qraw * c + qo * sn;
-                        krot = kraw * c + ko * sn;
-                    } else {
-                        qrot = qraw * c - qo * sn;
-                        krot = kraw * c - ko * sn;
+            float part = 0.f;
+#pragma unroll
+            for (int e = 0; e < DPT; ++e) {
+                const int i = tid + e * NC; // head dimension of this thread
+                float qraw = 0.f, kraw = 0.f;
+                if (i < D) {
+                    qraw = load_input<D>(a, a.q, a.q_w_scale, unit, b, h, i);
+                    if (is_last) kraw = load_input<D>(a, a.k, a.k_w_scale, unit, b, h, i);
+                }
+                float qrot = qraw, krot = kraw;
+                if (a.freq_cis) {
+                    // pairs (2i, 2i+1) sit in neighbouring lanes of one warp
+                    const float qo = __shfl_xor_sync(0xffffffffu, qraw, 1);
+                    const float ko = __shfl_xor_sync(0xffffffffu, kraw, 1);
+                    if (i < D) {
+                        const int row = a.rope_pos0 + (a.rope_add_past ? past : 0);
+                        const float *fr = a.freq_cis + (size_t)row * D;
+                        const float c = __ldg(fr + (i & ~1)), sn = __ldg(fr + (i | 1));
+                        if (i & 1) {
+                            qrot = qraw * c + qo * sn;
+                            krot = kraw * c + ko * sn;
+                        } else {
+                            qrot = qraw * c - qo * sn;
+                            krot = kraw * c - ko * sn;
+                        }
                     }
                 }
-            }
-            float part = 0.f;
-            if (tid < D) {
-                const float qs = qrot * a.scale_log2e;
-                q_s[tid] = qs;
-                if (is_last) {
-                    const float kr = CacheIO<CacheT>::round(krot);
-                    krot_keep = krot;
-                    part = qs * kr;
+                krot_keep[e] = 0.f;
+                if (i < D) {
+                    const float qs = qrot * a.scale_log2e;
+                    q_s[i] = qs;
+                    if (is_last) {
+                        const float kr = CacheIO<CacheT>::round(krot);
+                        krot_keep[e] = krot;
+                        part += qs * kr;
+                    }
                 }
             }
             if (is_last) {
@@ -303,16 +315,20 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
             }
         }
 
-        const int c = lane % LPR;   // 16-byte chunk of the row this lane owns
+        const int c = lane % LPR;   // first 16-byte chunk of the row this lane owns (then c + LPR, ...)
         const int sub = lane / LPR; // which of the RPI rows of a step
-        float qreg[EPL];
+        float qreg[CPL][EPL];
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) qreg[j] = q_s[c * EPL + j];
+        for (int k = 0; k < CPL; ++k)
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) qreg[k][j] = q_s[(c + k * LPR) * EPL + j];
 
         float m_run = kMaxInit, l_run = 0.f;
-        float o[EPL];
+        float o[CPL][EPL];
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) o[j] = 0.f;
+        for (int k = 0; k < CPL; ++k)
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) o[k][j] = 0.f;
 
         const float *mask_row = (a.mask_mode == 1) ? a.attn_mask + (size_t)past * a.mask_row_stride + row0 : nullptr;
 
@@ -333,12 +349,15 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
 #pragma unroll
             for (int it = 0; it < ITERS; ++it) {
                 const int r = (it * NWARPS + warp) * RPI + sub;
-                const uint4 kv = *reinterpret_cast<const uint4 *>(Kt + (size_t)r * D + c * EPL);
-                float kf[EPL];
-                CacheIO<CacheT>::unpack(kv, kf);
                 float acc = 0.f;
 #pragma unroll
-                for (int j = 0; j < EPL; ++j) acc = fmaf(qreg[j], kf[j], acc);
+                for (int k = 0; k < CPL; ++k) {
+                    const uint4 kv = *reinterpret_cast<const uint4 *>(Kt + (size_t)r * D + (c + k * LPR) * EPL);
+                    float kf[EPL];
+                    CacheIO<CacheT>::unpack(kv, kf);
+#pragma unroll
+                    for (int j = 0; j < EPL; ++j) acc = fmaf(qreg[k][j], kf[j], acc);
+                }
                 sc[it] = acc;
             }
 #pragma unroll
@@ -357,24 +376,30 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
                 }
                 mt = fmaxf(mt, sc[it]);
             }
-            if (RPI == 2) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
+#pragma unroll
+            for (int off = 16; off >= LPR; off >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, off)); // the warp's RPI rows
             const float m_new = fmaxf(m_run, mt);
             const float corr = ex2(m_run - m_new);
             m_run = m_new;
             l_run *= corr;
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) o[j] *= corr;
+            for (int k = 0; k < CPL; ++k)
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) o[k][j] *= corr;
 #pragma unroll
             for (int it = 0; it < ITERS; ++it) {
                 const int r = (it * NWARPS + warp) * RPI + sub;
                 if (r < rvalid) {
                     const float p = ex2(sc[it] - m_new);
                     l_run += p;
-                    const uint4 vv = *reinterpret_cast<const uint4 *>(Vt + (size_t)r * D + c * EPL);
-                    float vf[EPL];
-                    CacheIO<CacheT>::unpack(vv, vf);
 #pragma unroll
-                    for (int j = 0; j < EPL; ++j) o[j] = fmaf(p, vf[j], o[j]);
+                    for (int k = 0; k < CPL; ++k) {
+                        const uint4 vv = *reinterpret_cast<const uint4 *>(Vt + (size_t)r * D + (c + k * LPR) * EPL);
+                        float vf[EPL];
+                        CacheIO<CacheT>::unpack(vv, vf);
+#pragma unroll
+                        for (int j = 0; j < EPL; ++j) o[k][j] = fmaf(p, vf[j], o[k][j]);
+                    }
                 }
             }
             __syncwarp();
@@ -385,23 +410,35 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
         //    this one must have completed (a no-op unless the launch was an early-start one)
         if (a.early_start == 2) grid_dependency_wait();
         if (bad_len && tid == 0 && split == 0) atomicOr(a.status, 4u);
-        if (is_last && tid < D) {
+        if (is_last) {
             // a3, a4 of the reference: dequantise v, round k and v to the cache type, append row `past`
-            const float vraw = load_input(a, a.v, a.v_w_scale, unit, b, h, tid);
-            vnew = CacheIO<CacheT>::round(vraw);
-            const size_t cidx = ((size_t)unit * a.T + past) * D + tid;
-            CacheIO<CacheT>::store((CacheT *)a.k_cache + cidx, krot_keep);
-            CacheIO<CacheT>::store((CacheT *)a.v_cache + cidx, vraw);
+#pragma unroll
+            for (int e = 0; e < DPT; ++e) {
+                const int i = tid + e * NC;
+                if (i < D) {
+                    const float vraw = load_input<D>(a, a.v, a.v_w_scale, unit, b, h, i);
+                    vnew[e] = CacheIO<CacheT>::round(vraw);
+                    const size_t cidx = ((size_t)unit * a.T + past) * D + i;
+                    CacheIO<CacheT>::store((CacheT *)a.k_cache + cidx, krot_keep[e]);
+                    CacheIO<CacheT>::store((CacheT *)a.v_cache + cidx, vraw);
+                }
+            }
         }
 
-        if (RPI == 2) {
-            l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
+        // the warp's RPI rows of a step fold into one partial per chunk
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) o[j] += __shfl_xor_sync(0xffffffffu, o[j], 16);
+        for (int off = 16; off >= LPR; off >>= 1) {
+            l_run += __shfl_xor_sync(0xffffffffu, l_run, off);
+#pragma unroll
+            for (int k = 0; k < CPL; ++k)
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) o[k][j] += __shfl_xor_sync(0xffffffffu, o[k][j], off);
         }
         if (sub == 0) {
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) wo[warp * D + c * EPL + j] = o[j];
+            for (int k = 0; k < CPL; ++k)
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) wo[warp * D + (c + k * LPR) * EPL + j] = o[k][j];
         }
         if (lane == 0) {
             wm[warp] = m_run;
@@ -411,38 +448,47 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
     __syncthreads();
 
     // ---------------- merge the compute warps (warp order), add the new token ----------------
+    // compute thread t finishes head dimensions t, t + NC, ...
     const int tid = threadIdx.x;
-    float acc = 0.f, lsum = 0.f, M = kMaxInit;
-    if (tid < D) {
+    float acc[DPT], lsum = 0.f, M = kMaxInit;
+#pragma unroll
+    for (int e = 0; e < DPT; ++e) acc[e] = 0.f;
+    if (tid < NC) {
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, wm[w]);
         if (is_last && new_visible) M = fmaxf(M, s_new);
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) {
-            const float e = ex2(wm[w] - M);
-            acc = fmaf(wo[w * D + tid], e, acc);
-            lsum = fmaf(wl[w], e, lsum);
+            const float e2 = ex2(wm[w] - M);
+#pragma unroll
+            for (int e = 0; e < DPT; ++e)
+                if (tid + e * NC < D) acc[e] = fmaf(wo[w * D + tid + e * NC], e2, acc[e]);
+            lsum = fmaf(wl[w], e2, lsum);
         }
         if (is_last && new_visible) {
             const float p = ex2(s_new - M);
-            acc = fmaf(p, vnew, acc);
+#pragma unroll
+            for (int e = 0; e < DPT; ++e) acc[e] = fmaf(p, vnew[e], acc[e]);
             lsum += p;
         }
     }
 
     if (nsplit == 1) {
-        if (tid < D) {
-            const float r = (lsum > 0.f) ? acc / lsum : 0.f;
-            store_out_element(a, unit, tid, r);
+        if (tid < NC) {
+#pragma unroll
+            for (int e = 0; e < DPT; ++e)
+                if (tid + e * NC < D) store_out_element<D>(a, unit, tid + e * NC, (lsum > 0.f) ? acc[e] / lsum : 0.f);
         }
-        if (a.out_q8) quantize_row_if_last<NWARPS>(a, b, red, flag);
+        if (a.out_q8) quantize_row_if_last<D, NWARPS>(a, b, red, flag);
         return;
     }
 
     // ---------------- split-KV: publish the partial, the last arriver merges ------------------
     const size_t pbase = (size_t)unit * a.nsplit_max;
-    if (tid < D) {
-        a.part_o[(pbase + split) * D + tid] = acc;
+    if (tid < NC) {
+#pragma unroll
+        for (int e = 0; e < DPT; ++e)
+            if (tid + e * NC < D) a.part_o[(pbase + split) * D + tid + e * NC] = acc[e];
         if (tid == 0) {
             a.part_ml[(pbase + split) * 2 + 0] = M;
             a.part_ml[(pbase + split) * 2 + 1] = lsum;
@@ -457,30 +503,35 @@ __global__ void __launch_bounds__((NWARPS + 1) * 32) flb_decode_attn_kernel(cons
     __syncthreads();
     if (!*flag) return;
     __threadfence();
-    if (tid < D) {
+    if (tid < NC) {
         float M2 = kMaxInit;
         for (int i = 0; i < nsplit; ++i) M2 = fmaxf(M2, __ldcg(a.part_ml + (pbase + i) * 2));
-        float acc2 = 0.f, l2 = 0.f;
+        float acc2[DPT], l2 = 0.f;
+#pragma unroll
+        for (int e = 0; e < DPT; ++e) acc2[e] = 0.f;
         for (int i = 0; i < nsplit; ++i) {
-            const float e = ex2(__ldcg(a.part_ml + (pbase + i) * 2) - M2);
-            acc2 = fmaf(__ldcg(a.part_o + (pbase + i) * D + tid), e, acc2);
-            l2 = fmaf(__ldcg(a.part_ml + (pbase + i) * 2 + 1), e, l2);
+            const float e2 = ex2(__ldcg(a.part_ml + (pbase + i) * 2) - M2);
+#pragma unroll
+            for (int e = 0; e < DPT; ++e)
+                if (tid + e * NC < D) acc2[e] = fmaf(__ldcg(a.part_o + (pbase + i) * D + tid + e * NC), e2, acc2[e]);
+            l2 = fmaf(__ldcg(a.part_ml + (pbase + i) * 2 + 1), e2, l2);
         }
-        const float r = (l2 > 0.f) ? acc2 / l2 : 0.f;
-        store_out_element(a, unit, tid, r);
+#pragma unroll
+        for (int e = 0; e < DPT; ++e)
+            if (tid + e * NC < D) store_out_element<D>(a, unit, tid + e * NC, (l2 > 0.f) ? acc2[e] / l2 : 0.f);
         if (tid == 0) a.counters[unit] = 0u; // ready for the next call
     }
-    if (a.out_q8) quantize_row_if_last<NWARPS>(a, b, red, flag);
+    if (a.out_q8) quantize_row_if_last<D, NWARPS>(a, b, red, flag);
 }
 
 // ---- host-side launcher ------------------------------------------------------------------
 
-template <typename CacheT, int TILE_ROWS, int STAGES, int NWARPS>
+template <typename CacheT, int HD, int TILE_ROWS, int STAGES, int NWARPS>
 static cudaError_t launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
-    constexpr int TILE_BYTES = TILE_ROWS * kHeadDim * (int)sizeof(CacheT);
+    constexpr int TILE_BYTES = TILE_ROWS * HD * (int)sizeof(CacheT);
     constexpr size_t smem = (size_t)STAGES * 2 * TILE_BYTES + 2 * STAGES * sizeof(uint64_t) +
-                            sizeof(float) * (kHeadDim + 2 * NWARPS + NWARPS * kHeadDim + NWARPS) + 16;
-    auto kern = flb_decode_attn_kernel<CacheT, TILE_ROWS, STAGES, NWARPS>;
+                            sizeof(float) * (HD + 2 * NWARPS + NWARPS * HD + NWARPS) + 16;
+    auto kern = flb_decode_attn_kernel<CacheT, HD, TILE_ROWS, STAGES, NWARPS>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const unsigned grid = (unsigned)a.B * (unsigned)a.H * (unsigned)a.nsplit_max;
@@ -501,12 +552,20 @@ static cudaError_t launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
-cudaError_t launch_decode(const DecodeArgs &a, bool cache_f16, cudaStream_t stream) {
-    // Two 32-row (fp16) / 16-row (fp32) stages = 32 KB of ring per CTA, so that 6 CTAs share an SM:
-    // measured on B200, many small rings beat few deep ones (each CTA's prologue and merge overlap
-    // the other CTAs' streaming); deeper rings (4, 6 stages) lost 15-40 % of the bandwidth.
-    if (cache_f16) return launch_decode_t<__half, 32, 2, 4>(a, stream);
-    return launch_decode_t<float, 16, 2, 4>(a, stream);
+cudaError_t launch_decode(const DecodeArgs &a, bool cache_f16, int head_dim, cudaStream_t stream) {
+    // Two stages of 8 KB K + 8 KB V tiles (32 rows of 128 halves, 16 rows of 128 floats, ...) = 32 KB of ring per
+    // CTA, so that 6 CTAs share an SM: measured on B200 at head size 128, many small rings beat few deep ones
+    // (each CTA's prologue and merge overlap the other CTAs' streaming); deeper rings (4, 6 stages) lost 15-40 %
+    // of the bandwidth.  The other head sizes the reference's kernels accept up to 256
+    // (decoder_kernels.cu:563-589) keep the tile's byte size.
+    if (cache_f16) {
+        if (head_dim == 64) return launch_decode_t<__half, 64, 64, 2, 4>(a, stream);
+        if (head_dim == 256) return launch_decode_t<__half, 256, 16, 2, 4>(a, stream);
+        return launch_decode_t<__half, 128, 32, 2, 4>(a, stream);
+    }
+    if (head_dim == 64) return launch_decode_t<float, 64, 32, 2, 4>(a, stream);
+    if (head_dim == 256) return launch_decode_t<float, 256, 8, 2, 4>(a, stream);
+    return launch_decode_t<float, 128, 16, 2, 4>(a, stream);
 }
 
 } // namespace flb

@@ -8,7 +8,7 @@
 #include <cuda_runtime.h>
 
 namespace flb {
-cudaError_t launch_decode(const DecodeArgs &a, bool cache_f16, cudaStream_t stream);
+cudaError_t launch_decode(const DecodeArgs &a, bool cache_f16, int head_dim, cudaStream_t stream);
 }
 
 namespace {
@@ -31,14 +31,14 @@ inline int nsplit_for(int past, int split_len) { return past <= 0 ? 1 : (past + 
 struct ScratchLayout {
     size_t counter_bytes, ml_off, o_off, total;
 };
-inline ScratchLayout layout_for(int B, int H, int nsplit_max) {
+inline ScratchLayout layout_for(int B, int H, int nsplit_max, int head_dim = flb::kHeadDim) {
     ScratchLayout l;
     const size_t units = (size_t)B * H;
     // status words, one arrival counter per (b,h) (partition merge), one per sequence (fused quantisation)
     l.counter_bytes = round_up(sizeof(unsigned) * (flb::kStatusWords + units + (size_t)B), 256);
     l.ml_off = l.counter_bytes;
     l.o_off = l.ml_off + round_up(units * nsplit_max * 2 * sizeof(float), 256);
-    l.total = l.o_off + units * nsplit_max * flb::kHeadDim * sizeof(float);
+    l.total = l.o_off + units * nsplit_max * head_dim * sizeof(float);
     return l;
 }
 
@@ -47,7 +47,10 @@ int check_common(const flb_attn_params *p) {
     if (p->batch_size <= 0 || p->head_num <= 0 || p->size_per_head <= 0 || p->seq_len <= 0 || p->total_len <= 0)
         return FLB_ERR_BAD_SHAPE;
     if (p->start_pos < 0) return FLB_ERR_BAD_SHAPE;
-    if (p->size_per_head != flb::kHeadDim) return FLB_ERR_UNSUPPORTED;
+    // decode: the head sizes up to 256 that the reference's kernels accept in steps of the warp size
+    // (decoder_kernels.cu:563-589); the tensor-core prefill kernel is built for 128
+    if (p->size_per_head != flb::kHeadDim && !(p->seq_len == 1 && (p->size_per_head == 64 || p->size_per_head == 256)))
+        return FLB_ERR_UNSUPPORTED;
     if (p->input_mode < FLB_IN_INT32 || p->input_mode > FLB_IN_F16) return FLB_ERR_BAD_ENUM;
     if (p->mask_mode < FLB_MASK_NONE || p->mask_mode > FLB_MASK_CAUSAL_STRICT) return FLB_ERR_BAD_ENUM;
     if (p->cache_dtype != FLB_F32 && p->cache_dtype != FLB_F16) return FLB_ERR_BAD_ENUM;
@@ -128,7 +131,7 @@ int flb_attn_validate(const flb_attn_params *p) {
         if (!aligned16(p->scratch)) return FLB_ERR_MISALIGNED;
         const int nsm = nsplit_for(mp, split_len_of(p));
         if ((unsigned long long)p->batch_size * p->head_num * nsm > 0x7fffffffull) return FLB_ERR_TOO_LARGE; // grid / int indices
-        const ScratchLayout l = layout_for(p->batch_size, p->head_num, nsm);
+        const ScratchLayout l = layout_for(p->batch_size, p->head_num, nsm, p->size_per_head);
         if (p->scratch_bytes < l.total) return FLB_ERR_SCRATCH_TOO_SMALL;
     } else {
         // the reference's prefill attends over the fresh rows only (open_decoder.cu:181-190)
@@ -157,7 +160,7 @@ int flb_attn_workspace_bytes(const flb_attn_params *p, size_t *bytes_out) {
     if (p->split_len < 0 || (p->split_len % 32) != 0) return FLB_ERR_BAD_SHAPE;
     // worst case over every call these dimensions allow: a decode step on a full cache, or a
     // prefill of seq_len tokens
-    const size_t dec = layout_for(p->batch_size, p->head_num, nsplit_for(p->total_len - 1, split_len_of(p))).total;
+    const size_t dec = layout_for(p->batch_size, p->head_num, nsplit_for(p->total_len - 1, split_len_of(p)), p->size_per_head > 0 ? p->size_per_head : flb::kHeadDim).total;
     const size_t pre = p->seq_len > 1 ? flb::prefill_scratch_bytes(p->batch_size, p->head_num, p->seq_len) : 0;
     *bytes_out = dec > pre ? dec : pre;
     return FLB_OK;
@@ -171,7 +174,7 @@ int flb_attn_decode(const flb_attn_params *p, void *cuda_stream) {
 
     const int split_len = split_len_of(p);
     const int nsplit_max = nsplit_for(max_past_of(p), split_len);
-    const ScratchLayout l = layout_for(p->batch_size, p->head_num, nsplit_max);
+    const ScratchLayout l = layout_for(p->batch_size, p->head_num, nsplit_max, p->size_per_head);
     unsigned char *sc = static_cast<unsigned char *>(p->scratch);
 
     if (!p->scratch_zeroed) {
@@ -190,7 +193,7 @@ int flb_attn_decode(const flb_attn_params *p, void *cuda_stream) {
     a.q = p->q;
     a.k = p->k;
     a.v = p->v;
-    a.row_stride = p->qkv_row_stride ? p->qkv_row_stride : p->head_num * flb::kHeadDim;
+    a.row_stride = p->qkv_row_stride ? p->qkv_row_stride : p->head_num * p->size_per_head;
     a.act_scale = p->act_scale;
     a.q_w_scale = p->q_w_scale;
     a.k_w_scale = p->k_w_scale;
@@ -219,7 +222,7 @@ int flb_attn_decode(const flb_attn_params *p, void *cuda_stream) {
     a.part_ml = reinterpret_cast<float *>(sc + l.ml_off);
     a.part_o = reinterpret_cast<float *>(sc + l.o_off);
 
-    if (flb::launch_decode(a, p->cache_dtype == FLB_F16, stream) != cudaSuccess) return FLB_ERR_LAUNCH;
+    if (flb::launch_decode(a, p->cache_dtype == FLB_F16, p->size_per_head, stream) != cudaSuccess) return FLB_ERR_LAUNCH;
     return FLB_OK;
 }
 

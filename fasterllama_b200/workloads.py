@@ -85,7 +85,7 @@ class Case:
         e_c = 2 if "16" in str(a["k_cache"].dtype) else 4
         e_in = {"int32": 4, "float32": 4, "float16": 2}[str(a["q"].dtype).replace("torch.", "")]
         e_out = 2 if "16" in str(a["out"].dtype) else 4
-        d = HEAD_DIM
+        d = int(a["q"].shape[-1])
         if "past_lens" in a and a["past_lens"] is not None:
             pl = a["past_lens"]
             lens = pl.cpu().numpy() if hasattr(pl, "cpu") else np.asarray(pl)
@@ -111,12 +111,12 @@ def host_case(
     mask_mode: int = A.FLB_MASK_CAUSAL_INCLUSIVE,
     split_len: int = 0,
     uniform_start_pos: bool | None = None,
+    d: int = HEAD_DIM,
 ) -> Case:
     """Draws a case with numpy.  `past` is an int (same cached length for every sequence, the
     reference's start_pos) or an int array [B] (per-sequence lengths).  `rope`: "past" rotates at
     the absolute position, "reference" at the chunk-relative row like the reference, "none"."""
     rng = np.random.default_rng(seed)
-    d = HEAD_DIM
     per_seq = not np.isscalar(past)
     lens = np.asarray(past, dtype=np.int32) if per_seq else np.full(B, int(past), dtype=np.int32)
     if uniform_start_pos is None:
@@ -153,7 +153,7 @@ def host_case(
     c = Case(
         name=name, B=B, H=H, S=S, T=T, start_pos=int(lens[0]) if uniform_start_pos else 0, arrays=arrays,
         rope_pos0=0, rope_add_past=(rope == "past"), mask_mode=mask_mode, split_len=split_len,
-        max_past_len=int(lens.max()) if not uniform_start_pos else 0,
+        max_past_len=int(lens.max()) if not uniform_start_pos else 0, softmax_scale=1.0 / math.sqrt(d),
     )
     c.meta["seed"] = seed
     return c
@@ -170,7 +170,7 @@ def to_device(case: Case, device: str = "cuda:0") -> dict[str, Any]:
         buf = dev["_merged"]
         for i, name in enumerate(("q", "k", "v")):
             dev[name] = buf[:, :, i * H * d:(i + 1) * H * d].unflatten(2, (H, d))
-    n = A.workspace_bytes(case.B, case.H, case.T, case.S, case.split_len)
+    n = A.workspace_bytes(case.B, case.H, case.T, case.S, case.split_len, size_per_head=int(case.arrays["q"].shape[-1]))
     dev["scratch"] = torch.empty(n, dtype=torch.uint8, device=device)
     return dev
 

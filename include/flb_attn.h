@@ -78,7 +78,7 @@ typedef struct flb_attn_params {
     /* dimensions (names follow OpenDecoder's constructor, open_decoder.h:65) */
     int batch_size;    /* B                                                              */
     int head_num;      /* H                                                              */
-    int size_per_head; /* d; this build supports 128                                     */
+    int size_per_head; /* d: 128; decode calls (seq_len == 1) also take 64 and 256       */
     int seq_len;       /* S, tokens of this call per sequence: 1 = decode, >1 = prefill  */
     int start_pos;     /* rows already in the cache, same for every sequence
                           (OpenDecoder::forward's start_pos)                             */

@@ -31,6 +31,21 @@ CASES = {
 }
 
 
+# Decode at the other head sizes the call accepts (the reference's kernels take them too: size_per_head <= 128 on
+# its warp kernels, 256 on its block kernels, decoder_kernels.cu:563-589).  Their vectors live in a fixture of their
+# own, ref_golden_head_sizes.npz, made by `make_ref_golden.py <out> head_sizes`.
+HEAD_SIZE_CASES = {
+    "decode_d64_L200_inclusive": dict(B=2, H=8, S=1, T=256, start_pos=199, mask="inclusive", rope_row=199, d=64),
+    "decode_d64_L700_strict": dict(B=1, H=8, S=1, T=768, start_pos=699, mask="strict", rope_row=0, d=64),
+    "decode_d256_L150_none": dict(B=2, H=8, S=1, T=192, start_pos=149, mask="none", rope_row=149, d=256),
+    "decode_d256_L600_inclusive": dict(B=1, H=8, S=1, T=640, start_pos=599, mask="inclusive", rope_row=599, d=256),
+}
+
+
+def case(name: str) -> dict:
+    return CASES[name] if name in CASES else HEAD_SIZE_CASES[name]
+
+
 # heads whose results the fixture keeps for the prefill cases
 PREFILL_HEADS_KEPT = (0, 5)
 
@@ -58,8 +73,9 @@ def _centered_sum(n: int, salt: int, terms: int, span: int) -> np.ndarray:
 def build(name: str) -> dict:
     """Host arrays of one golden case (everything but the RoPE table rows, which the fixture
     stores because they come from the reference's own table kernel)."""
-    c = CASES[name]
+    c = case(name)
     B, H, S, T, sp = c["B"], c["H"], c["S"], c["T"], c["start_pos"]
+    D = c.get("d", globals()["D"])  # head size of this case
     salt = sum(ord(ch) for ch in c.get("inputs_of", name))  # "inputs_of": share another case's inputs
     n = B * S * H * D
     a = {}

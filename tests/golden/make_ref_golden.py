@@ -2,7 +2,8 @@
 cuBLAS calls (oracle/_ref/libflb_ref.so, built by oracle/build_ref.sh from the reference checkout)
 on the deterministic inputs of golden_cases.py.  Needs a GPU:
 
-    python tests/golden/make_ref_golden.py <output.npz>
+    python tests/golden/make_ref_golden.py <output.npz>                  (ref_golden.npz: the head-size-128 cases)
+    python tests/golden/make_ref_golden.py <output.npz> head_sizes       (ref_golden_head_sizes.npz: decode at 64 and 256)
 
 Stored per case (prefill cases: for the heads in golden_cases.PREFILL_HEADS_KEPT only, to keep
 the fixture small): the attention output, the cache rows the call appended, the RoPE table rows it
@@ -27,14 +28,15 @@ import golden_cases as G  # noqa: E402
 from oracle.ref_runner import RefRunner  # noqa: E402
 
 
-def main(out_path: str) -> None:
+def main(out_path: str, which: str = "base") -> None:
     ref = RefRunner()
     store: dict[str, np.ndarray] = {}
     notes: dict[str, object] = {"torch": torch.__version__, "gpu": torch.cuda.get_device_name(0)}
-    for name, c in G.CASES.items():
+    cases = G.HEAD_SIZE_CASES if which == "head_sizes" else G.CASES
+    for name, c in cases.items():
         a = G.build(name)
         t = {k: torch.from_numpy(v).cuda() for k, v in a.items()}
-        table = ref.freq_cis(c["T"] + 8)
+        table = ref.freq_cis(c["T"] + 8, c.get("d", G.D))
         t["freq_cis"] = table
         args = ref.make_args(t, start_pos=c["start_pos"], rope_row=c["rope_row"], as_written=c.get("as_written", False))
         st = ref.attention(args)
@@ -47,6 +49,12 @@ def main(out_path: str) -> None:
         store[f"{name}/freq_rows"] = table[c["rope_row"]:c["rope_row"] + S].cpu().numpy()
         notes[name] = {"status": st, "nan_rows": int(torch.isnan(t["out"]).any(dim=-1).sum())}
         print(name, "status", st, "nan rows", notes[name]["nan_rows"], flush=True)
+    if which == "head_sizes":
+        store["notes_json"] = np.frombuffer(json.dumps(notes).encode(), dtype=np.uint8)
+        np.savez_compressed(out_path, **store)
+        print("wrote", out_path, os.path.getsize(out_path), "bytes")
+        ref.close()
+        return
     # what the reference's decode call does, exactly as written, at L = 257 (> size_per_head)
     name = "decode_config1_shape"
     a = G.build(name)
@@ -64,4 +72,4 @@ def main(out_path: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "ref_golden.npz"))
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "ref_golden.npz"), sys.argv[2] if len(sys.argv) > 2 else "base")

@@ -24,11 +24,29 @@ _GOLD = None
 REF_PREFILL_ABS = 5e-3
 
 
+class _Fixtures:
+    """The committed fixtures as one mapping: ref_golden.npz (head size 128) and ref_golden_head_sizes.npz."""
+
+    def __init__(self):
+        self.files = [np.load(os.path.join(HERE, "golden", n)) for n in ("ref_golden.npz", "ref_golden_head_sizes.npz")
+                      if os.path.exists(os.path.join(HERE, "golden", n))]
+
+    def __getitem__(self, key):
+        for f in self.files:
+            if key in f.files:
+                return f[key]
+        raise KeyError(key)
+
+
 def gold():
     global _GOLD
     if _GOLD is None:
-        _GOLD = np.load(os.path.join(HERE, "golden", "ref_golden.npz"))
+        _GOLD = _Fixtures()
     return _GOLD
+
+
+def head_size_fixture_present() -> bool:
+    return os.path.exists(os.path.join(HERE, "golden", "ref_golden_head_sizes.npz"))
 
 
 def notes() -> dict:
@@ -39,11 +57,12 @@ def case_from_golden(name: str, mask_mode: str = "generic", cache_dtype: str = "
     """The golden case `name` as call parameters.  `mask_mode`: "generic" hands over the additive
     [T,T] mask exactly like the reference; "index" uses the index-computed mode that the mask
     classifies as."""
-    c = G.CASES[name]
+    c = G.case(name)
     a = G.build(name)
     S, T, sp = c["S"], c["T"], c["start_pos"]
+    d = c.get("d", G.D)
     # table with the stored rows placed where the call will look for them
-    table = np.zeros((T + 8, G.D), dtype=np.float32)
+    table = np.zeros((T + 8, d), dtype=np.float32)
     table[c["rope_row"]:c["rope_row"] + S] = gold()[f"{name}/freq_rows"]
     a["freq_cis"] = table
     if cache_dtype != "float32":
@@ -58,7 +77,7 @@ def case_from_golden(name: str, mask_mode: str = "generic", cache_dtype: str = "
         mm = A.FLB_MASK_CAUSAL_STRICT if c["mask"] == "strict" else A.FLB_MASK_CAUSAL_INCLUSIVE
         a.pop("attn_mask", None)
     return W.Case(name=name, B=c["B"], H=c["H"], S=S, T=T, start_pos=sp, arrays=a,
-                  rope_pos0=c["rope_row"], rope_add_past=False, mask_mode=mm)
+                  rope_pos0=c["rope_row"], rope_add_past=False, mask_mode=mm, softmax_scale=1.0 / float(np.sqrt(d)))
 
 
 def compare_with_golden(name: str, out: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, *, tol_out_abs: float | None,
@@ -67,7 +86,7 @@ def compare_with_golden(name: str, out: np.ndarray, k_cache: np.ndarray, v_cache
     reference produced NaN (fully masked rows: 0/0 in its softmax) must be exactly zero here."""
     from util import assert_abs_close, assert_fp32_close
 
-    c = G.CASES[name]
+    c = G.case(name)
     S, sp = c["S"], c["start_pos"]
     hs = list(G.PREFILL_HEADS_KEPT) if S > 1 else list(range(c["H"]))
     want = gold()[f"{name}/out"]
