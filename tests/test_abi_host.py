@@ -62,7 +62,7 @@ def test_validate_accepts_a_good_block_and_names_each_fault():
     assert A.validate(p) == _lib.FLB_ERR_NULL_POINTER
     p = c.params(); p.scratch = None
     assert A.validate(p) == _lib.FLB_ERR_NULL_POINTER
-    p = c.params(); p.size_per_head = 64
+    p = c.params(); p.size_per_head = 96  # decode takes 64, 128 and 256
     assert A.validate(p) == _lib.FLB_ERR_UNSUPPORTED
     p = c.params(); p.batch_size = 0
     assert A.validate(p) == _lib.FLB_ERR_BAD_SHAPE
