@@ -178,7 +178,7 @@ def compare_logits(variants: list[str], cfg: dict, mask: str = "inclusive", devi
                   "max_abs_diff_first_step": float(per_step[0]), "max_abs_diff_last_step": float(per_step[-1]),
                   "top4_set_same": float(same_set.float().mean()), "argmax_same": float(same_arg.float().mean()),
                   "steps_with_all_top4_sets_same": float(same_set.all(dim=1).float().mean()),
-                  "median_4th_to_5th_gap": float(gap.median())}
+                  "median_4th_to_5th_gap": float(gap[torch.isfinite(gap)].median()) if bool(torch.isfinite(gap).any()) else None}
         del lg
     return out
 
