@@ -18,9 +18,10 @@
 //    an atomic counter, heavy (late) query blocks first, in groups of heads whose K/V stay in L2.  Key tiles hold 64
 //    keys.  TMEM (512 columns): per query tile two score buffers of 64 columns (fp32 scores; P overwrites them as
 //    fp16 pairs) and 128 columns of fp32 accumulator O.  Warp roles:
-//      warp 0      work scheduler + K/V loader: TMA boxes (128-byte swizzle) into one ring whose stage holds the K
-//                  tile and the V tile of the same 64 keys; a stage is free again once both query tiles' P.V over
-//                  it have retired
+//      warp 0      work scheduler + K/V loader: TMA boxes (128-byte swizzle) into a ring of K tiles and a ring of V
+//                  tiles (64 keys each).  A K tile goes back to the loader when both query tiles' S over it have
+//                  landed, a V tile when both query tiles' P.V over it have retired: K is needed two tiles earlier
+//                  than V and is free two tiles earlier, so two rings of three stages do what one ring of five did
 //      warps 1, 3  issue S = Q_t.K_j^T for query tile 0 / 1 (SS form: both operands in shared memory, 128 x 64 x 16
 //                  per instruction) and load that tile's query rows.  S runs TWO key tiles ahead of P.V: while
 //                  the softmax threads work on S_j, S_{j+1} is already in TMEM, so they never wait for the pipe;
@@ -58,14 +59,20 @@ constexpr int TILE_BYTES = BM * D * 2;    // query tile: 128 rows of fp16 = 32 K
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int KV_TILE_BYTES = BN * D * 2; // K or V tile: 64 keys = 16 KB, two [64 x 64] swizzled blocks
 constexpr int KV_HALF_BYTES = KV_TILE_BYTES / 2;
-constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES; // one ring stage: the K tile and the V tile of the same 64 keys
-#ifndef FLB_PF_KV_STAGES
-#define FLB_PF_KV_STAGES 5
+#ifndef FLB_PF_K_STAGES
+#define FLB_PF_K_STAGES 3
+#endif
+#ifndef FLB_PF_V_STAGES
+#define FLB_PF_V_STAGES 3
 #endif
 #ifndef FLB_PF_EMUL
 #define FLB_PF_EMUL 0
 #endif
-constexpr int KV_STAGES = FLB_PF_KV_STAGES; // a stage is free again once both query tiles' O += P.V over it have completed
+// Two rings of 64-key tiles.  A K tile is needed two tiles earlier than the V tile of the same keys (S runs two tiles
+// ahead of P.V) and is free again as soon as both query tiles' S over it have landed; a V tile is free once both query
+// tiles' P.V over it have retired.  Separate rings give each the depth it needs in 96 KB instead of 128-160 KB.
+constexpr int K_STAGES = FLB_PF_K_STAGES;
+constexpr int V_STAGES = FLB_PF_V_STAGES;
 constexpr int kExpOnFmaEvery = FLB_PF_EMUL; // every n-th exponential of a row on the FMA pipe (0 = none)
 constexpr int NUM_THREADS = 512;          // warps: 0 scheduler + K loads, 1 MMA, 2 V loads, 3 Q loads, 4-11 softmax, 12-15 epilogue
 constexpr uint32_t TMEM_COLS = 512;       // per query tile: two score buffers of 64 columns + 128 columns of O
@@ -253,7 +260,8 @@ constexpr int kHeadsPerGroup = 32;    // work list: groups of this many (b,h) un
 
 struct __align__(8) PrefillBarriers {
     uint64_t q_full[2], q_empty[2];   // per query tile of the item
-    uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES]; // K and V tile of 64 keys landed / both query tiles are done with them
+    uint64_t k_full[K_STAGES], k_empty[K_STAGES]; // K tile landed / S of both query tiles over it has landed (2 arrivals)
+    uint64_t v_full[V_STAGES], v_empty[V_STAGES]; // V tile landed / P.V of both query tiles over it has retired
     uint64_t s_full[2][2];            // [t][buffer] S = Q_t.K_j^T landed in score buffer j & 1 of query tile t
     uint64_t p_full[2][2];            // [t][buffer] P_j written over the scores by the 128 softmax threads of query tile t
     uint64_t pv_done[2][2];           // [t][buffer] O_t += P_j.V_j retired: score buffer j & 1 may take S_{j+2}
@@ -265,7 +273,7 @@ struct __align__(8) PrefillBarriers {
     int abort_flag;
 };
 constexpr int kBarrierSlot = 512;
-constexpr size_t kPrefillSmem = 2 * (size_t)TILE_BYTES + (size_t)KV_STAGES * STAGE_BYTES + 2 * BM * sizeof(float) + kBarrierSlot;
+constexpr size_t kPrefillSmem = 2 * (size_t)TILE_BYTES + (size_t)(K_STAGES + V_STAGES) * KV_TILE_BYTES + 2 * BM * sizeof(float) + kBarrierSlot;
 static_assert(sizeof(PrefillBarriers) <= kBarrierSlot, "barrier block must fit its slot");
 static_assert(kPrefillSmem <= 232448, "exceeds the 227 KB a CTA may use");
 
@@ -373,8 +381,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     // The 128-byte swizzle pattern is a function of address bits [4,10): tiles must start on 1 KB.
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char *sQ = smem;                                  // two query tiles
-    unsigned char *sKV = sQ + 2 * TILE_BYTES;                  // K/V ring: stage = K tile, then V tile
-    float *l_buf = reinterpret_cast<float *>(sKV + KV_STAGES * STAGE_BYTES); // [2][128] row sums of the item being finished
+    unsigned char *sK = sQ + 2 * TILE_BYTES;                   // K ring
+    unsigned char *sV = sK + K_STAGES * KV_TILE_BYTES;         // V ring
+    float *l_buf = reinterpret_cast<float *>(sV + V_STAGES * KV_TILE_BYTES); // [2][128] row sums of the item being finished
     PrefillBarriers *pb = reinterpret_cast<PrefillBarriers *>(l_buf + 2 * BM);
     if (smem_u32(smem) & 1023u) { // never observed; without it the MMAs would read scrambled tiles
         grid_dependency_wait();
@@ -401,9 +410,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             mbar_init(&pb->l_full[t], BM);
             mbar_init(&pb->l_empty[t], BM);
         }
-        for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(&pb->kv_full[s], 1);
-            mbar_init(&pb->kv_empty[s], 1); // the P.V issuer: both query tiles' products over it have retired
+        for (int s = 0; s < K_STAGES; ++s) {
+            mbar_init(&pb->k_full[s], 1);
+            mbar_init(&pb->k_empty[s], 2); // per query tile: its softmax warps once S has landed, or its S issuer for a tile it skips
+        }
+        for (int s = 0; s < V_STAGES; ++s) {
+            mbar_init(&pb->v_full[s], 1);
+            mbar_init(&pb->v_empty[s], 1); // the P.V issuer: both query tiles' products over it have retired
         }
         for (int s = 0; s < SCHED_DEPTH; ++s) {
             mbar_init(&pb->sched_full[s], 1);
@@ -473,14 +486,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 return k < (unsigned)num_items ? (int)k : -1;
             };
             auto load_k = [&](int bh, int j) -> bool {
-                const uint32_t s = kt % KV_STAGES;
-                if (!wait_bar(&pb->kv_empty[s], ((kt / KV_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
-                unsigned char *dst = sKV + s * STAGE_BYTES;
-                mbar_arrive_expect_tx(&pb->kv_full[s], STAGE_BYTES);
-                tma_load_3d(dst, &tmK, 0, j * BN, bh, &pb->kv_full[s]);
-                tma_load_3d(dst + KV_HALF_BYTES, &tmK, 64, j * BN, bh, &pb->kv_full[s]);
-                tma_load_3d(dst + KV_TILE_BYTES, &tmV, 0, j * BN, bh, &pb->kv_full[s]);
-                tma_load_3d(dst + KV_TILE_BYTES + KV_HALF_BYTES, &tmV, 64, j * BN, bh, &pb->kv_full[s]);
+                const uint32_t ks = kt % K_STAGES, vs = kt % V_STAGES;
+                if (!wait_bar(&pb->k_empty[ks], ((kt / K_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
+                unsigned char *dk = sK + ks * KV_TILE_BYTES;
+                mbar_arrive_expect_tx(&pb->k_full[ks], KV_TILE_BYTES);
+                tma_load_3d(dk, &tmK, 0, j * BN, bh, &pb->k_full[ks]);
+                tma_load_3d(dk + KV_HALF_BYTES, &tmK, 64, j * BN, bh, &pb->k_full[ks]);
+                if (!wait_bar(&pb->v_empty[vs], ((kt / V_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
+                unsigned char *dv = sV + vs * KV_TILE_BYTES;
+                mbar_arrive_expect_tx(&pb->v_full[vs], KV_TILE_BYTES);
+                tma_load_3d(dv, &tmV, 0, j * BN, bh, &pb->v_full[vs]);
+                tma_load_3d(dv + KV_HALF_BYTES, &tmV, 64, j * BN, bh, &pb->v_full[vs]);
                 ++kt;
                 return true;
             };
@@ -514,7 +530,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const uint32_t tS_t = tmem + (uint32_t)(t * 128);
             // descriptor start addresses count 16-byte units
             const uint64_t dq0 = umma_desc_sw128(smem_u32(sQ) + t * TILE_BYTES, 16, 1024);
-            const uint64_t dk0 = umma_desc_sw128(smem_u32(sKV), 16, 1024);
+            const uint64_t dk0 = umma_desc_sw128(smem_u32(sK), 16, 1024);
             uint64_t *const q_full = &pb->q_full[t], *const q_empty = &pb->q_empty[t], *const s_full = &pb->s_full[t][0],
                             *const pv_done = &pb->pv_done[t][0];
             unsigned char *const sQ_t = sQ + t * TILE_BYTES;
@@ -545,11 +561,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     ++nq;
                     continue;
                 }
-                const uint32_t ks = kt % KV_STAGES;
-                ok = wait_bar(&pb->kv_full[ks], (kt / KV_STAGES) & 1u, pb, a.status);
+                const uint32_t ks = kt % K_STAGES;
+                ok = wait_bar(&pb->k_full[ks], (kt / K_STAGES) & 1u, pb, a.status);
                 if (!ok) break;
                 ++kt;
-                if (j >= n_t) { // above this query tile's diagonal
+                if (j >= n_t) { // above this query tile's diagonal: nothing of this tile is read on its behalf
+                    mbar_arrive(&pb->k_empty[ks]);
                     ++j;
                     continue;
                 }
@@ -558,7 +575,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (ok && gs >= 2) ok = wait_bar(pv_done + buf, ((gs - 2u) >> 1) & 1u, pb, a.status); // P_{j-2}.V_{j-2} has read this buffer
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t dk = dk0 + (uint64_t)(ks * (uint32_t)(STAGE_BYTES >> 4));
+                const uint64_t dk = dk0 + (uint64_t)(ks * (uint32_t)(KV_TILE_BYTES >> 4));
                 const uint32_t ts = tS_t + buf * (uint32_t)BN;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) { // dims 16 kk .. 16 kk + 15
@@ -580,7 +597,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         // apart (LBO), 8-key groups 1024 B apart (SBO)).  The stage goes back to the loader when both have retired.
         if (lane == 0) {
             constexpr uint32_t idesc_pv = umma_idesc_f16(BM, D, false, true);
-            const uint64_t dv0 = umma_desc_sw128(smem_u32(sKV) + KV_TILE_BYTES, KV_HALF_BYTES, 1024);
+            const uint64_t dv0 = umma_desc_sw128(smem_u32(sV), KV_HALF_BYTES, 1024);
             uint32_t taken = 0, vt = 0, gp[2] = {0, 0}, ci[2] = {0, 0};
             int nmax = 0, n[2] = {0, 0}, j = 0;
             bool ok = true;
@@ -598,9 +615,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     j = 0;
                     continue;
                 }
-                // No wait for the stage: a P exists only after its S, whose issuer has waited for the stage to land.
-                const uint32_t vs = vt % KV_STAGES;
-                const uint64_t dv = dv0 + (uint64_t)(vs * (uint32_t)(STAGE_BYTES >> 4));
+                const uint32_t vs = vt % V_STAGES;
+                ok = wait_bar(&pb->v_full[vs], (vt / V_STAGES) & 1u, pb, a.status);
+                if (!ok) break;
+                const uint64_t dv = dv0 + (uint64_t)(vs * (uint32_t)(KV_TILE_BYTES >> 4));
                 ++vt;
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
@@ -625,7 +643,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     ++gp[t];
                 }
                 if (!ok) break;
-                umma_commit(&pb->kv_empty[vs]);
+                umma_commit(&pb->v_empty[vs]);
                 ++j;
             }
         }
@@ -639,7 +657,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const uint32_t tS_t = tmem + (uint32_t)(t * 128), tO_t = tmem + 256u + (uint32_t)(t * D);
         uint64_t *const s_full = &pb->s_full[t][0], *const pv_done = &pb->pv_done[t][0], *const l_full = &pb->l_full[t],
                         *const l_empty = &pb->l_empty[t], *const p_full = &pb->p_full[t][0];
-        uint32_t taken = 0, ct = 0, ci = 0;
+        uint32_t taken = 0, ct = 0, ci = 0, kbase = 0; // kbase: K-ring tiles of the items before this one
+        const bool k_releaser = (quarter == 0 && lane == 0); // one thread per query tile hands K tiles back to the loader
         bool ok = true;
         for (;;) {
             int bh, qb;
@@ -652,7 +671,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (bh < 0) break;
             const ItemGeom g = item_geom(qb, a.S, causal);
             const int n_t = t ? g.n[1] : g.n[0];
-            if (n_t == 0) continue;
             const int q0 = t ? g.q0[1] : g.q0[0], row = q0 + lrow;
             float m_used = -1e30f;
             float2 l2 = make_float2(0.f, 0.f);
@@ -666,6 +684,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
+                // S_j has landed, so this query tile's product has finished reading K_j (the issuer hands back the tiles
+                // it skips itself; the other query tile's share comes from its own softmax warps)
+                if (k_releaser) mbar_arrive(&pb->k_empty[(kbase + (uint32_t)j) % K_STAGES]);
                 const uint32_t ts = tS_t + buf * (uint32_t)BN + lane_addr;
                 tmem_ld32(ts, ra);
                 tmem_ld32(ts + 32, rb);
@@ -738,6 +759,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             l_buf[t * BM + lrow] = l2.x + l2.y;
             mbar_arrive(l_full);
             ++ci;
+            kbase += (uint32_t)g.nmax;
         }
     } else {
         // ======================= epilogue: warps 12-15, O_t / l -> global =======================
