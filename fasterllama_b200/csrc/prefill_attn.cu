@@ -74,7 +74,7 @@ constexpr int KV_HALF_BYTES = KV_TILE_BYTES / 2;
 constexpr int K_STAGES = FLB_PF_K_STAGES;
 constexpr int V_STAGES = FLB_PF_V_STAGES;
 constexpr int kExpOnFmaEvery = FLB_PF_EMUL; // every n-th exponential of a row on the FMA pipe (0 = none)
-constexpr int NUM_THREADS = 512;          // warps: 0 scheduler + K loads, 1 MMA, 2 V loads, 3 Q loads, 4-11 softmax, 12-15 epilogue
+constexpr int NUM_THREADS = 512;          // warps: 0 scheduler + K/V loads, 1 and 3 S issue + Q loads, 2 P.V issue, 4-11 softmax, 12-15 epilogue
 constexpr uint32_t TMEM_COLS = 512;       // per query tile: two score buffers of 64 columns + 128 columns of O
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f; // log2 domain: P stays below 2^8, exact in fp16 range
@@ -594,7 +594,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         // ======================= P.V issuer (both query tiles) =======================
         // O_t (+)= P_j.V_j for t = 0, 1 over every ring tile: P read from TMEM as the A operand (fp16 pairs in the
         // columns S came from), V from shared memory as an MN-major B operand (the two 64-dim blocks KV_HALF_BYTES
-        // apart (LBO), 8-key groups 1024 B apart (SBO)).  The stage goes back to the loader when both have retired.
+        // apart (LBO), 8-key groups 1024 B apart (SBO)).  The V stage goes back to the loader when both have retired.
         if (lane == 0) {
             constexpr uint32_t idesc_pv = umma_idesc_f16(BM, D, false, true);
             const uint64_t dv0 = umma_desc_sw128(smem_u32(sV), KV_HALF_BYTES, 1024);
