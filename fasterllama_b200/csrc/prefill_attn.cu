@@ -21,7 +21,10 @@
 //      warp 0      work scheduler + K/V loader: TMA boxes (128-byte swizzle) into a ring of K tiles and a ring of V
 //                  tiles (64 keys each).  A K tile goes back to the loader when both query tiles' S over it have
 //                  landed, a V tile when both query tiles' P.V over it have retired: K is needed two tiles earlier
-//                  than V and is free two tiles earlier, so two rings of three stages do what one ring of five did
+//                  than V and is free two tiles earlier, so two rings do in 96-128 KB what one ring needed 160 KB for.
+//                  With fp16 inputs and an fp16 cache the V tiles come straight from the caller's v (a rank-4 tensor
+//                  map over its [B,S,H,d] rows) and the loader stores them into the cache from the ring (TMA store)
+//                  when their stage comes up for reuse: the streaming pass in front then moves q and k only
 //      warps 1, 3  issue S = Q_t.K_j^T for query tile 0 / 1 (SS form: both operands in shared memory, 128 x 64 x 16
 //                  per instruction) and load that tile's query rows.  S runs TWO key tiles ahead of P.V: while
 //                  the softmax threads work on S_j, S_{j+1} is already in TMEM, so they never wait for the pipe;
@@ -60,17 +63,18 @@ constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int KV_TILE_BYTES = BN * D * 2; // K or V tile: 64 keys = 16 KB, two [64 x 64] swizzled blocks
 constexpr int KV_HALF_BYTES = KV_TILE_BYTES / 2;
 #ifndef FLB_PF_K_STAGES
-#define FLB_PF_K_STAGES 3
+#define FLB_PF_K_STAGES 4
 #endif
 #ifndef FLB_PF_V_STAGES
-#define FLB_PF_V_STAGES 3
+#define FLB_PF_V_STAGES 4
 #endif
 #ifndef FLB_PF_EMUL
 #define FLB_PF_EMUL 0
 #endif
 // Two rings of 64-key tiles.  A K tile is needed two tiles earlier than the V tile of the same keys (S runs two tiles
 // ahead of P.V) and is free again as soon as both query tiles' S over it have landed; a V tile is free once both query
-// tiles' P.V over it have retired.  Separate rings give each the depth it needs in 96 KB instead of 128-160 KB.
+// tiles' P.V over it have retired.  Three stages each already match one ring of five K+V stages; four each leave room for
+// the V tiles' way into the cache (below) and for the longer latency of V tiles read from the caller's strided rows.
 constexpr int K_STAGES = FLB_PF_K_STAGES;
 constexpr int V_STAGES = FLB_PF_V_STAGES;
 constexpr int kExpOnFmaEvery = FLB_PF_EMUL; // every n-th exponential of a row on the FMA pipe (0 = none)
@@ -100,6 +104,8 @@ struct PrefillArgs {
     int out_f16;
     float scale_log2e;
     unsigned *status;
+    int v_direct; // fp16 v into an fp16 cache: nothing to convert, so the attention kernel takes the V tiles straight from the
+                  // caller's v and stores them into the cache itself; the streaming pass leaves v alone
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -205,7 +211,7 @@ template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_
         const size_t in_off = ((size_t)b * a.S + s) * a.row_stride + (size_t)h * D + c * 8;
         rq[r] = load_raw8<MODE>(a.q, in_off);
         rk[r] = load_raw8<MODE>(a.k, in_off);
-        rv[r] = load_raw8<MODE>(a.v, in_off);
+        if (!(MODE == 2 && a.v_direct)) rv[r] = load_raw8<MODE>(a.v, in_off);
         as[r] = (MODE == 0) ? __ldg(a.act_scale + (size_t)b * a.S + s) : 1.0f;
         if (a.freq_cis) {
             const float4 *fr = reinterpret_cast<const float4 *>(a.freq_cis + (size_t)(a.rope_pos0 + s) * D + c * 8);
@@ -233,7 +239,7 @@ template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_
             float q[8], k[8], v[8];
             convert8<MODE>(rq[r], as[r], wq0, wq1, q);
             convert8<MODE>(rk[r], as[r], wk0, wk1, k);
-            convert8<MODE>(rv[r], as[r], wv0, wv1, v);
+            if (!(MODE == 2 && a.v_direct)) convert8<MODE>(rv[r], as[r], wv0, wv1, v);
             if (a.freq_cis) {
                 rope8(f0[r], f1[r], q);
                 rope8(f0[r], f1[r], k);
@@ -242,7 +248,7 @@ template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_
             const size_t ca_off = (bh * a.T + s) * D + c * 8; // [B,H,T,d]
             *reinterpret_cast<uint4 *>(a.qh + st_off) = pack8(q);
             store_cache8(a, a.k_cache, ca_off, k);
-            store_cache8(a, a.v_cache, ca_off, v);
+            if (!(MODE == 2 && a.v_direct)) store_cache8(a, a.v_cache, ca_off, v);
             if (!a.cache_f16) {
                 *reinterpret_cast<uint4 *>(a.kh + st_off) = pack8(k);
                 *reinterpret_cast<uint4 *>(a.vh + st_off) = pack8(v);
@@ -269,6 +275,7 @@ struct __align__(8) PrefillBarriers {
     uint64_t l_full[2], l_empty[2];   // row sums of an item in shared memory / read by the epilogue
     uint64_t sched_full[SCHED_DEPTH], sched_empty[SCHED_DEPTH];
     int sched_bh[SCHED_DEPTH], sched_qb[SCHED_DEPTH]; // the published items; bh < 0 = no more work
+    int v_store_bh[V_STAGES], v_store_j[V_STAGES];    // loader's notes: the V tile in stage s still has to go into the cache (bh < 0: not)
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -377,7 +384,8 @@ __device__ __forceinline__ void chunk_exp(const uint32_t (&r)[32], float scale, 
 template <int EMUL>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     flb_prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                            const __grid_constant__ CUtensorMap tmV, const PrefillArgs a, const int num_items) {
+                            const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmVin, const PrefillArgs a,
+                            const int num_items) {
     // The 128-byte swizzle pattern is a function of address bits [4,10): tiles must start on 1 KB.
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char *sQ = smem;                                  // two query tiles
@@ -423,10 +431,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             mbar_init(&pb->sched_empty[s], kSchedConsumers);
         }
         pb->abort_flag = 0;
+        for (int s = 0; s < V_STAGES; ++s) pb->v_store_bh[s] = -1;
         mbar_fence_init();
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
+        if (a.v_direct) tma_prefetch_desc(&tmVin);
     }
     if (warp == 1) {
         tmem_alloc(&pb->tmem_base, TMEM_COLS);
@@ -485,19 +495,62 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 const unsigned k = gridDim.x + atomicAdd(counter, 1u);
                 return k < (unsigned)num_items ? (int)k : -1;
             };
-            auto load_k = [&](int bh, int j) -> bool {
-                const uint32_t ks = kt % K_STAGES, vs = kt % V_STAGES;
+            // V tiles that come straight from the caller's v (fp16 into an fp16 cache) also have to be appended to the cache:
+            // the item that covers every key tile of its unit (the last query block) sends each of its V tiles on with a
+            // TMA store, out of the stage, when the stage comes up for reuse — by then both P.V products have read it.
+            auto store_v = [&](uint32_t vs) {
+                const int sbh = pb->v_store_bh[vs];
+                if (sbh < 0) return;
+                const int sj = pb->v_store_j[vs];
+                unsigned char *dv = sV + vs * KV_TILE_BYTES;
+                tma_store_3d(&tmV, dv, 0, sj * BN, sbh);
+                tma_store_3d(&tmV, dv + KV_HALF_BYTES, 64, sj * BN, sbh);
+                bulk_commit_group();
+                bulk_wait_group_read_all(); // the stage is about to be overwritten
+                pb->v_store_bh[vs] = -1;
+            };
+            // The V tile of a key tile is wanted two tiles later than its K tile, so the loader issues it one step late:
+            // K_j, then V_{j-1} (across items as well).  Whatever the V stage costs on its way to reuse — the wait for
+            // both P.V products, the store into the cache — then never sits in front of a K load.
+            int late_bh = -1, late_j = 0;
+            bool late_keeper = false;
+            uint32_t vt = 0;
+            auto load_v_late = [&]() -> bool {
+                if (late_bh < 0) return true;
+                const uint32_t vs = vt % V_STAGES;
+                if (!wait_bar(&pb->v_empty[vs], ((vt / V_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
+                unsigned char *dv = sV + vs * KV_TILE_BYTES;
+                if (a.v_direct) {
+                    store_v(vs);
+                    if (late_keeper) {
+                        pb->v_store_bh[vs] = late_bh;
+                        pb->v_store_j[vs] = late_j;
+                    }
+                    const int b = late_bh / a.H, h = late_bh - b * a.H;
+                    mbar_arrive_expect_tx(&pb->v_full[vs], KV_TILE_BYTES);
+                    tma_load_4d(dv, &tmVin, 0, late_j * BN, h, b, &pb->v_full[vs]);
+                    tma_load_4d(dv + KV_HALF_BYTES, &tmVin, 64, late_j * BN, h, b, &pb->v_full[vs]);
+                } else {
+                    mbar_arrive_expect_tx(&pb->v_full[vs], KV_TILE_BYTES);
+                    tma_load_3d(dv, &tmV, 0, late_j * BN, late_bh, &pb->v_full[vs]);
+                    tma_load_3d(dv + KV_HALF_BYTES, &tmV, 64, late_j * BN, late_bh, &pb->v_full[vs]);
+                }
+                ++vt;
+                late_bh = -1;
+                return true;
+            };
+            auto load_k = [&](int bh, int j, bool keeper) -> bool {
+                const uint32_t ks = kt % K_STAGES;
                 if (!wait_bar(&pb->k_empty[ks], ((kt / K_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
                 unsigned char *dk = sK + ks * KV_TILE_BYTES;
                 mbar_arrive_expect_tx(&pb->k_full[ks], KV_TILE_BYTES);
                 tma_load_3d(dk, &tmK, 0, j * BN, bh, &pb->k_full[ks]);
                 tma_load_3d(dk + KV_HALF_BYTES, &tmK, 64, j * BN, bh, &pb->k_full[ks]);
-                if (!wait_bar(&pb->v_empty[vs], ((kt / V_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
-                unsigned char *dv = sV + vs * KV_TILE_BYTES;
-                mbar_arrive_expect_tx(&pb->v_full[vs], KV_TILE_BYTES);
-                tma_load_3d(dv, &tmV, 0, j * BN, bh, &pb->v_full[vs]);
-                tma_load_3d(dv + KV_HALF_BYTES, &tmV, 64, j * BN, bh, &pb->v_full[vs]);
                 ++kt;
+                if (!load_v_late()) return false;
+                late_bh = bh;
+                late_j = j;
+                late_keeper = keeper;
                 return true;
             };
             int cur = (int)blockIdx.x; // < num_items: the grid never exceeds the item count
@@ -507,10 +560,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 int bh, qb;
                 decode(cur, bh, qb);
                 const ItemGeom g = item_geom(qb, a.S, causal);
-                ok = load_k(bh, 0);
+                const bool keeper = (qb == nqb - 1); // its query rows see every key tile of the unit
+                ok = load_k(bh, 0, keeper);
                 if (ok) ok = publish(nxt); // one item of look-ahead for the other roles
-                for (int j = 1; j < g.nmax && ok; ++j) ok = load_k(bh, j);
+                for (int j = 1; j < g.nmax && ok; ++j) ok = load_k(bh, j, keeper);
                 cur = nxt;
+            }
+            if (ok) ok = load_v_late(); // the last V tile
+            if (a.v_direct && ok) {
+                // the tiles still in the ring: each goes out once its products have retired, and everything sent has
+                // to have arrived before the kernel ends
+                for (int i = 0; i < V_STAGES && ok; ++i, ++vt) {
+                    const uint32_t vs = vt % V_STAGES;
+                    ok = wait_bar(&pb->v_empty[vs], ((vt / V_STAGES) & 1u) ^ 1u, pb, a.status);
+                    if (ok) store_v(vs);
+                }
+                bulk_wait_group_all();
             }
         }
         __syncwarp();
@@ -925,6 +990,7 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     a.out_f16 = (p->out_dtype == FLB_F16);
     a.scale_log2e = p->softmax_scale * kLog2e;
     a.status = reinterpret_cast<unsigned *>(sc);
+    a.v_direct = (a.input_mode == FLB_IN_F16 && a.cache_f16) ? 1 : 0;
 
     CUtensorMap tmQ, tmK, tmV;
     bool ok = make_map(enc, &tmQ, a.qh, B * H, S, S, BM);
@@ -932,6 +998,16 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
         ok = ok && make_map(enc, &tmK, p->k_cache, B * H, S, T, BN) && make_map(enc, &tmV, p->v_cache, B * H, S, T, BN);
     } else {
         ok = ok && make_map(enc, &tmK, a.kh, B * H, S, S, BN) && make_map(enc, &tmV, a.vh, B * H, S, S, BN);
+    }
+    // the caller's v as a [batch][head][token][128] view of its [B,S,H,d] rows, for the V tiles taken from it directly
+    CUtensorMap tmVin = tmV;
+    if (ok && a.v_direct) {
+        const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+        const cuuint64_t strides[3] = {(cuuint64_t)a.row_stride * 2, (cuuint64_t)D * 2, (cuuint64_t)S * a.row_stride * 2};
+        const cuuint32_t box[4] = {64, (cuuint32_t)BN, 1, 1};
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        ok = enc(&tmVin, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(a.v), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
     }
     if (!ok) return FLB_ERR_LAUNCH;
     const int sms = current_device_sm_count();
@@ -968,7 +1044,7 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     cfg.gridDim = dim3((unsigned)(num_items < sms ? num_items : sms));
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = kPrefillSmem;
-    if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, a, (int)num_items) != cudaSuccess) return FLB_ERR_LAUNCH;
+    if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, tmVin, a, (int)num_items) != cudaSuccess) return FLB_ERR_LAUNCH;
     if (p->out_q8) {
         flb_attn_quant_transpose_kernel<<<dim3((unsigned)S, (unsigned)B), 128, 0, stream>>>((const float *)p->out, p->out_q8,
                                                                                            p->out_q8_scale, H, S);
