@@ -28,6 +28,8 @@
 #include "decode_attn.cuh"
 #include "flb_ptx.cuh"
 
+#include <atomic>
+
 namespace flb {
 
 namespace {
@@ -532,8 +534,18 @@ static cudaError_t launch_decode_t(const DecodeArgs &a, cudaStream_t stream) {
     constexpr size_t smem = (size_t)STAGES * 2 * TILE_BYTES + 2 * STAGES * sizeof(uint64_t) +
                             sizeof(float) * (HD + 2 * NWARPS + NWARPS * HD + NWARPS) + 16;
     auto kern = flb_decode_attn_kernel<CacheT, HD, TILE_ROWS, STAGES, NWARPS>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // the shared-memory opt-in is a property of (kernel, device): set once per device, not on every call (it costs about
+    // a microsecond of host time, which an isolated call sees in full)
+    static std::atomic<unsigned long long> opted_in{0};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
+    const unsigned long long bit = (dev >= 0 && dev < 64) ? (1ull << dev) : 0ull;
+    if (!(opted_in.load(std::memory_order_acquire) & bit)) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        if (bit) opted_in.fetch_or(bit, std::memory_order_release);
+    }
     const unsigned grid = (unsigned)a.B * (unsigned)a.H * (unsigned)a.nsplit_max;
     if (!a.early_start) {
         kern<<<grid, (NWARPS + 1) * 32, smem, stream>>>(a);

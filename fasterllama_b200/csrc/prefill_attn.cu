@@ -51,6 +51,8 @@
 
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 namespace flb {
 
 namespace {
@@ -936,10 +938,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_fn() {
-    void *fn = nullptr;
+    // the driver entry point does not change during the life of the process: looked up once
+    static std::atomic<void *> cached{nullptr};
+    void *fn = cached.load(std::memory_order_acquire);
+    if (fn) return reinterpret_cast<EncodeTiledFn>(fn);
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess) return nullptr;
-    if (qres != cudaDriverEntryPointSuccess) return nullptr;
+    if (qres != cudaDriverEntryPointSuccess || !fn) return nullptr;
+    cached.store(fn, std::memory_order_release);
     return reinterpret_cast<EncodeTiledFn>(fn);
 }
 
