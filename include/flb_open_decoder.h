@@ -354,7 +354,7 @@ static inline void flb_tp_push_setup(flb_tp_ctx *s, size_t slot_bytes, cudaStrea
         if (ok) FLB_TP_CUDA(cudaMemsetAsync(own, 0, total, stream), ok);
         if (ok) FLB_TP_CUDA(cudaIpcGetMemHandle(&mine, own), ok);
     }
-    /* handles (64 bytes each) and the verdict go through the communicator: the ranks stay in step whatever happened */
+    /* handles (64 bytes each) and the ranks' common decision go through the communicator: the ranks stay in step whatever happened */
     if (cudaMalloc((void **)&stage, (size_t)(g + 1) * 64 + 16) != cudaSuccess) {
         printf("flb_tp_push_setup: cudaMalloc failed\n");
         exit(1);
@@ -372,19 +372,19 @@ static inline void flb_tp_push_setup(flb_tp_ctx *s, size_t slot_bytes, cudaStrea
             ok = 0;
         }
     }
-    int *verdict = (int *)(stage + (size_t)(g + 1) * 64);
+    int *decision = (int *)(stage + (size_t)(g + 1) * 64);
     int mine_ok = ok;
-    if (cudaMemcpyAsync(verdict, &mine_ok, sizeof(int), cudaMemcpyHostToDevice, stream) != cudaSuccess) {
-        printf("flb_tp_push_setup: the verdict could not be staged\n");
+    if (cudaMemcpyAsync(decision, &mine_ok, sizeof(int), cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+        printf("flb_tp_push_setup: the decision could not be staged\n");
         exit(1);
     }
-    FLB_TP_NCCL(ncclAllReduce(verdict, verdict, 1, ncclInt, ncclMin, s->comm, stream));
-    if (cudaMemcpyAsync(&ok, verdict, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+    FLB_TP_NCCL(ncclAllReduce(decision, decision, 1, ncclInt, ncclMin, s->comm, stream));
+    if (cudaMemcpyAsync(&ok, decision, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
         cudaStreamSynchronize(stream) != cudaSuccess) {
-        printf("flb_tp_push_setup: the verdict could not be read back\n");
+        printf("flb_tp_push_setup: the decision could not be read back\n");
         exit(1);
     }
-    cudaGetLastError(); /* a failed IPC call above is handled by the verdict, not left as a sticky error text */
+    cudaGetLastError(); /* a failed IPC call above is handled by the common decision, not left as a sticky error text */
     cudaFree(stage);
     s->push_slot_bytes = slot_bytes;
     s->push_epoch = 0;
