@@ -327,8 +327,13 @@ def main(ref_root: str | None = None) -> None:
     if not ref_root or not os.path.isdir(os.path.join(ref_root, "fasterLlama")):
         raise SystemExit("usage: make_e2e_variants.py <reference checkout> [variants...]  (or set FLB_REFERENCE_ROOT)")
     os.makedirs(OUT, exist_ok=True)
-    for name in (sys.argv[2:] or ["ref", "flb", "ref32", "mix", "tp", "opt"]):
-        print("built", build(name, ref_root))
+    names = sys.argv[2:] or ["ref", "flb", "ref32", "mix", "tp", "opt"]
+    # every variant has its own copy of the sources and its own output: the compiles run side by side
+    from concurrent.futures import ThreadPoolExecutor
+
+    with ThreadPoolExecutor(max_workers=min(len(names), os.cpu_count() or 1)) as pool:
+        for lib in pool.map(lambda n: build(n, ref_root), names):
+            print("built", lib)
 
 
 if __name__ == "__main__":
