@@ -757,7 +757,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 const uint32_t ts = tS_t + buf * (uint32_t)BN + lane_addr;
                 tmem_ld32(ts, ra);
                 tmem_ld32(ts + 32, rb);
-                const int mode = (a.mask_mode == 1) ? 2 : (((causal && k0 + BN - 1 > q0) || (k0 + BN > a.S)) ? 1 : 0);
+                // a warp whose 32 rows all lie at or below the tile's last key needs no diagonal test (k0 + 63 is never a
+                // multiple of 32, so the comparison is the same for the inclusive and the strict form)
+                const int mode = (a.mask_mode == 1) ? 2 : (((causal && k0 + BN - 1 > q0 + quarter * 32) || (k0 + BN > a.S)) ? 1 : 0);
                 // keys this row may see inside the tile: [0, lim)
                 int lim = min(BN, a.S - k0);
                 if (a.mask_mode == 2) lim = min(lim, row - k0 + 1);
