@@ -383,7 +383,9 @@ __device__ __forceinline__ void chunk_exp(const uint32_t (&r)[32], float scale, 
     }
 }
 
-template <int EMUL>
+// GENERIC_MASK: the caller's additive mask is read (mask_mode GENERIC); OUT_F16: the output element type.  Compile-time so
+// that each form carries only its own code: what the sixteen warps execute has to share the instruction cache.
+template <int EMUL, bool GENERIC_MASK, bool OUT_F16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     flb_prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                             const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmVin, const PrefillArgs a,
@@ -759,23 +761,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tmem_ld32(ts + 32, rb);
                 // a warp whose 32 rows all lie at or below the tile's last key needs no diagonal test (k0 + 63 is never a
                 // multiple of 32, so the comparison is the same for the inclusive and the strict form)
-                const int mode = (a.mask_mode == 1) ? 2 : (((causal && k0 + BN - 1 > q0 + quarter * 32) || (k0 + BN > a.S)) ? 1 : 0);
+                const int mode = GENERIC_MASK ? 2 : (((causal && k0 + BN - 1 > q0 + quarter * 32) || (k0 + BN > a.S)) ? 1 : 0);
                 // keys this row may see inside the tile: [0, lim)
                 int lim = min(BN, a.S - k0);
                 if (a.mask_mode == 2) lim = min(lim, row - k0 + 1);
                 if (a.mask_mode == 3) lim = min(lim, row - k0);
-                if (mode == 2 && row >= a.S) lim = 0; // rows beyond the prompt: no mask row to read
-                const float *mrow = (mode == 2) ? a.attn_mask + (size_t)min(row, a.S - 1) * a.mask_row_stride + k0 : nullptr;
+                if (GENERIC_MASK && row >= a.S) lim = 0; // rows beyond the prompt: no mask row to read
+                const float *mrow = GENERIC_MASK ? a.attn_mask + (size_t)min(row, a.S - 1) * a.mask_row_stride + k0 : nullptr;
                 tmem_wait_ld(ra, rb);
                 float sc = a.scale_log2e;
                 if (mode != 0) { // rare: the causal diagonal, the end of the prompt, or a caller-supplied mask
-                    if (mode == 1) {
-                        mask_chunk<false>(ra, 0, lim, sc, mrow);
-                        mask_chunk<false>(rb, 32, lim, sc, mrow);
-                    } else {
-                        mask_chunk<true>(ra, 0, lim, sc, mrow);
-                        mask_chunk<true>(rb, 32, lim, sc, mrow);
-                    }
+                    mask_chunk<GENERIC_MASK>(ra, 0, lim, sc, mrow);
+                    mask_chunk<GENERIC_MASK>(rb, 32, lim, sc, mrow);
                     sc = 1.0f;
                 }
                 // two independent chains: the maximum is a latency chain, not a throughput one; scale > 0 commutes with max
@@ -835,7 +832,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int quarter = warp & 3;
         const int lrow = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const int esz = a.out_f16 ? 2 : 4;
+        constexpr int esz = OUT_F16 ? 2 : 4;
         uint32_t taken = 0, ci[2] = {0, 0};
         bool ok = true;
         for (;;) {
@@ -870,7 +867,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         mbar_arrive(&pb->o_empty[t]);
                     }
                     if (row < a.S) {
-                        if (a.out_f16) {
+                        if (OUT_F16) {
                             uint4 *dst = reinterpret_cast<uint4 *>(gout + ch * 32 * 2);
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
@@ -1044,7 +1041,9 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     cudaLaunchAttribute pdl[1];
     pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     pdl[0].val.programmaticStreamSerializationAllowed = 1;
-    auto kern = flb_prefill_attn_kernel<kExpOnFmaEvery>;
+    const bool generic_mask = (a.mask_mode == FLB_MASK_GENERIC);
+    auto kern = generic_mask ? (a.out_f16 ? flb_prefill_attn_kernel<kExpOnFmaEvery, true, true> : flb_prefill_attn_kernel<kExpOnFmaEvery, true, false>)
+                             : (a.out_f16 ? flb_prefill_attn_kernel<kExpOnFmaEvery, false, true> : flb_prefill_attn_kernel<kExpOnFmaEvery, false, false>);
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefillSmem) != cudaSuccess) return FLB_ERR_LAUNCH;
     const long long num_items = (long long)B * H * ((S + 2 * BM - 1) / (2 * BM));
     cfg.attrs = pdl;
