@@ -93,7 +93,9 @@ typedef struct flb_attn_params {
     /* inputs.  Every pointer of this block is a device-addressable address.  For a decode call q, k, v,
      * the scales and `out` may also be PINNED HOST memory (cudaHostAlloc / cudaHostRegister: device-
      * addressable as it is): the kernel then reads the step's inputs and stores its result rows over
-     * the bus itself — one launch, no staging copies.  Caches and scratch belong in device memory. */
+     * the bus itself — one launch, no staging copies.  Caches and scratch belong in device memory, and so do the
+     * inputs of a prefill call (with half inputs and a half cache the call reads v in 64-row tiles, several times,
+     * while its attention kernel runs). */
     int input_mode;         /* flb_input_mode                                            */
     const void *q;          /* [B,S,H,d]                                                 */
     const void *k;          /* [B,S,H,d]                                                 */
