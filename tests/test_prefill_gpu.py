@@ -54,6 +54,20 @@ def test_prefill_mask_modes(cuda_device, mask_mode, S):
         assert not cuda["out"][:, :, 0].any()  # row 0 sees no key: zeros (the reference gives NaN)
 
 
+@pytest.mark.parametrize("mask_mode", [A.FLB_MASK_NONE, A.FLB_MASK_GENERIC, A.FLB_MASK_CAUSAL_INCLUSIVE, A.FLB_MASK_CAUSAL_STRICT])
+@pytest.mark.parametrize("S", [60, 256, 300, 700])
+def test_prefill_half_inputs_half_cache_every_mask(cuda_device, mask_mode, S):
+    """fp16 q/k/v into an fp16 cache: the V tiles are read from the caller's rows and appended to the cache by the attention
+    kernel itself (each key tile once, whatever the mask lets the query blocks see); the appended rows must be the input
+    bit for bit and the rows behind the prompt untouched."""
+    case = W.host_case(f"pv-direct{mask_mode}-S{S}", 650 + S, 2, 3, S + 70, S=S, past=0, in_dtype="float16", cache_dtype="float16",
+                       out_dtype="float16", mask_mode=mask_mode)
+    cuda, orc = run_cuda(case), run_oracle(case)
+    _check(case, cuda, orc, cache16=True)
+    v_in = np.transpose(case.arrays["v"].astype(np.float32), (0, 2, 1, 3))  # [B,S,H,d] -> [B,H,S,d]
+    assert np.array_equal(cuda["v_cache"][:, :, :S], v_in)
+
+
 @pytest.mark.parametrize("name", [c for c in GU.G.CASES if c.startswith("prefill")])
 @pytest.mark.parametrize("mask_mode", ["generic", "index"])
 def test_prefill_matches_reference_golden(cuda_device, name, mask_mode):
