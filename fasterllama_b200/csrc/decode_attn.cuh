@@ -6,7 +6,7 @@
 
 namespace flb {
 
-constexpr int kHeadDim = 128;          // size_per_head this build is specialised for
+constexpr int kHeadDim = 128;          // size_per_head of the benchmarked models; the default where a call gives none
 constexpr int kDefaultSplitLen = 512;  // cache rows per split-KV partition
 constexpr int kShortSlabRows = 1024;   // slabs of at most this many rows ...
 constexpr int kShortSlabSplitLen = 256; // ... are split into partitions of this many rows

@@ -47,9 +47,10 @@ int check_common(const flb_attn_params *p) {
     if (p->batch_size <= 0 || p->head_num <= 0 || p->size_per_head <= 0 || p->seq_len <= 0 || p->total_len <= 0)
         return FLB_ERR_BAD_SHAPE;
     if (p->start_pos < 0) return FLB_ERR_BAD_SHAPE;
-    // decode: the head sizes up to 256 that the reference's kernels accept in steps of the warp size
-    // (decoder_kernels.cu:563-589); the tensor-core prefill kernel is built for 128
-    if (p->size_per_head != flb::kHeadDim && !(p->seq_len == 1 && (p->size_per_head == 64 || p->size_per_head == 256)))
+    // decode: 64, 128 and 256 of the head sizes that the reference's kernels accept (decoder_kernels.cu:563-589);
+    // the tensor-core prefill kernel is built for 64 and 128 (256 would need more accumulator columns than TMEM has
+    // beside the scores of two query tiles)
+    if (p->size_per_head != 128 && p->size_per_head != 64 && !(p->seq_len == 1 && p->size_per_head == 256))
         return FLB_ERR_UNSUPPORTED;
     if (p->input_mode < FLB_IN_INT32 || p->input_mode > FLB_IN_F16) return FLB_ERR_BAD_ENUM;
     if (p->mask_mode < FLB_MASK_NONE || p->mask_mode > FLB_MASK_CAUSAL_STRICT) return FLB_ERR_BAD_ENUM;
@@ -141,7 +142,7 @@ int flb_attn_validate(const flb_attn_params *p) {
         if (p->mask_mode == FLB_MASK_GENERIC && p->mask_row_stride < p->seq_len) return FLB_ERR_BAD_SHAPE;
         if (!p->scratch) return FLB_ERR_NULL_POINTER;
         if (!aligned16(p->scratch)) return FLB_ERR_MISALIGNED;
-        if (p->scratch_bytes < flb::prefill_scratch_bytes(p->batch_size, p->head_num, p->seq_len))
+        if (p->scratch_bytes < flb::prefill_scratch_bytes(p->batch_size, p->head_num, p->seq_len, p->size_per_head))
             return FLB_ERR_SCRATCH_TOO_SMALL;
     }
     return FLB_OK;
@@ -161,7 +162,7 @@ int flb_attn_workspace_bytes(const flb_attn_params *p, size_t *bytes_out) {
     // worst case over every call these dimensions allow: a decode step on a full cache, or a
     // prefill of seq_len tokens
     const size_t dec = layout_for(p->batch_size, p->head_num, nsplit_for(p->total_len - 1, split_len_of(p)), p->size_per_head > 0 ? p->size_per_head : flb::kHeadDim).total;
-    const size_t pre = p->seq_len > 1 ? flb::prefill_scratch_bytes(p->batch_size, p->head_num, p->seq_len) : 0;
+    const size_t pre = p->seq_len > 1 ? flb::prefill_scratch_bytes(p->batch_size, p->head_num, p->seq_len, p->size_per_head > 0 ? p->size_per_head : flb::kHeadDim) : 0;
     *bytes_out = dec > pre ? dec : pre;
     return FLB_OK;
 }
@@ -243,9 +244,9 @@ int flb_attn_quantize(const float *attn, int8_t *q8, float *scale, int batch_siz
                       void *cuda_stream) {
     if (!attn || !q8 || !scale) return FLB_ERR_NULL_POINTER;
     if (batch_size <= 0 || head_num <= 0 || seq_len <= 0) return FLB_ERR_BAD_SHAPE;
-    if (size_per_head != flb::kHeadDim) return FLB_ERR_UNSUPPORTED;
+    if (size_per_head != 128 && size_per_head != 64) return FLB_ERR_UNSUPPORTED;
     if (batch_size > 65535) return FLB_ERR_TOO_LARGE; // grid.y
-    return flb::launch_quantize(attn, q8, scale, batch_size, head_num, seq_len, static_cast<cudaStream_t>(cuda_stream));
+    return flb::launch_quantize(attn, q8, scale, batch_size, head_num, seq_len, size_per_head, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int flb_attn_scratch_status(const void *scratch, unsigned *status_out, void *cuda_stream) {

@@ -57,13 +57,14 @@ namespace flb {
 
 namespace {
 
-constexpr int D = 128;       // head dimension
+// The head size is a template parameter (128, or 64): a tile is made of [rows x 64 dims] blocks in the 128-byte-swizzled
+// operand layout, one block per 64 head dimensions.
 constexpr int BM = 128;      // query rows per tile (two tiles per work item)
 constexpr int BN = 64;       // keys per K/V tile
-constexpr int TILE_BYTES = BM * D * 2;    // query tile: 128 rows of fp16 = 32 KB, two [128 x 64] swizzled blocks
-constexpr int HALF_BYTES = TILE_BYTES / 2;
-constexpr int KV_TILE_BYTES = BN * D * 2; // K or V tile: 64 keys = 16 KB, two [64 x 64] swizzled blocks
-constexpr int KV_HALF_BYTES = KV_TILE_BYTES / 2;
+constexpr int HALF_BYTES = BM * 64 * 2;    // one [128 x 64] block of a query tile: 16 KB
+constexpr int KV_HALF_BYTES = BN * 64 * 2; // one [64 x 64] block of a K or V tile: 8 KB
+constexpr int tile_bytes(int d) { return BM * d * 2; }    // query tile: 128 rows of fp16 (32 KB at d = 128)
+constexpr int kv_tile_bytes(int d) { return BN * d * 2; } // K or V tile: 64 keys (16 KB at d = 128)
 #ifndef FLB_PF_K_STAGES
 #define FLB_PF_K_STAGES 4
 #endif
@@ -193,11 +194,14 @@ __device__ __forceinline__ void rope8(const float4 &f0, const float4 &f1, float 
     }
 }
 
-template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_kernel(const PrefillArgs a) {
+template <int MODE, int HD> __global__ void __launch_bounds__(256) flb_prefill_prologue_kernel(const PrefillArgs a) {
     constexpr int R = kRowsPerThread;
-    const int sblocks = (a.S + 16 * R - 1) / (16 * R);
-    const int c = threadIdx.x & 15;
-    const int s0 = (int)(blockIdx.x % sblocks) * (16 * R) + (threadIdx.x >> 4);
+    constexpr int D = HD;
+    constexpr int TPR = D / 8;    // threads per token row
+    constexpr int RPP = 256 / TPR; // token rows a block covers per pass
+    const int sblocks = (a.S + RPP * R - 1) / (RPP * R);
+    const int c = threadIdx.x % TPR;
+    const int s0 = (int)(blockIdx.x % sblocks) * (RPP * R) + (threadIdx.x / TPR);
     const int h = (int)((blockIdx.x / sblocks) % a.H);
     const int b = (int)(blockIdx.x / ((size_t)sblocks * a.H));
     Raw8 rq[R], rk[R], rv[R];
@@ -210,7 +214,7 @@ template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_
     // ---- every load first
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int s = min(s0 + 16 * r, a.S - 1); // rows past the end load a valid row and are not stored
+        const int s = min(s0 + RPP * r, a.S - 1); // rows past the end load a valid row and are not stored
         const size_t in_off = ((size_t)b * a.S + s) * a.row_stride + (size_t)h * D + c * 8;
         rq[r] = load_raw8<MODE>(a.q, in_off);
         rk[r] = load_raw8<MODE>(a.k, in_off);
@@ -237,7 +241,7 @@ template <int MODE> __global__ void __launch_bounds__(256) flb_prefill_prologue_
     const size_t bh = (size_t)b * a.H + h;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int s = s0 + 16 * r;
+        const int s = s0 + RPP * r;
         if (s < a.S) {
             float q[8], k[8], v[8];
             convert8<MODE>(rq[r], as[r], wq0, wq1, q);
@@ -283,9 +287,11 @@ struct __align__(8) PrefillBarriers {
     int abort_flag;
 };
 constexpr int kBarrierSlot = 512;
-constexpr size_t kPrefillSmem = 2 * (size_t)TILE_BYTES + (size_t)(K_STAGES + V_STAGES) * KV_TILE_BYTES + 2 * BM * sizeof(float) + kBarrierSlot;
+constexpr size_t prefill_smem(int d) {
+    return 2 * (size_t)tile_bytes(d) + (size_t)(K_STAGES + V_STAGES) * kv_tile_bytes(d) + 2 * BM * sizeof(float) + kBarrierSlot;
+}
 static_assert(sizeof(PrefillBarriers) <= kBarrierSlot, "barrier block must fit its slot");
-static_assert(kPrefillSmem <= 232448, "exceeds the 227 KB a CTA may use");
+static_assert(prefill_smem(128) <= 232448, "exceeds the 227 KB a CTA may use");
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
@@ -386,12 +392,17 @@ __device__ __forceinline__ void chunk_exp(const uint32_t (&r)[32], float scale, 
 
 // GENERIC_MASK: the caller's additive mask is read (mask_mode GENERIC); OUT_F16: the output element type.  Compile-time so
 // that each form carries only its own code: what the sixteen warps execute has to share the instruction cache.
-template <int EMUL, bool GENERIC_MASK, bool OUT_F16>
+template <int EMUL, bool GENERIC_MASK, bool OUT_F16, int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     flb_prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                             const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmVin, const PrefillArgs a,
                             const int num_items) {
     // The 128-byte swizzle pattern is a function of address bits [4,10): tiles must start on 1 KB.
+    constexpr int D = HD;
+    constexpr int NBLK = D / 64;                      // 64-dim blocks per tile
+    constexpr int TILE_BYTES = BM * D * 2;
+    constexpr int KV_TILE_BYTES = BN * D * 2;
+    static_assert(D == 64 || D == 128, "O_t takes D TMEM columns per query tile beside the 256 columns of scores");
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char *sQ = smem;                                  // two query tiles
     unsigned char *sK = sQ + 2 * TILE_BYTES;                   // K ring
@@ -509,8 +520,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (sbh < 0) return;
                 const int sj = pb->v_store_j[vs];
                 unsigned char *dv = sV + vs * KV_TILE_BYTES;
-                tma_store_3d(&tmV, dv, 0, sj * BN, sbh);
-                tma_store_3d(&tmV, dv + KV_HALF_BYTES, 64, sj * BN, sbh);
+#pragma unroll
+                for (int blk = 0; blk < NBLK; ++blk) tma_store_3d(&tmV, dv + blk * KV_HALF_BYTES, 64 * blk, sj * BN, sbh);
                 bulk_commit_group();
                 bulk_wait_group_read_all(); // the stage is about to be overwritten
                 pb->v_store_bh[vs] = -1;
@@ -534,12 +545,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     }
                     const int b = late_bh / a.H, h = late_bh - b * a.H;
                     mbar_arrive_expect_tx(&pb->v_full[vs], KV_TILE_BYTES);
-                    tma_load_4d(dv, &tmVin, 0, late_j * BN, h, b, &pb->v_full[vs]);
-                    tma_load_4d(dv + KV_HALF_BYTES, &tmVin, 64, late_j * BN, h, b, &pb->v_full[vs]);
+#pragma unroll
+                    for (int blk = 0; blk < NBLK; ++blk)
+                        tma_load_4d(dv + blk * KV_HALF_BYTES, &tmVin, 64 * blk, late_j * BN, h, b, &pb->v_full[vs]);
                 } else {
                     mbar_arrive_expect_tx(&pb->v_full[vs], KV_TILE_BYTES);
-                    tma_load_3d(dv, &tmV, 0, late_j * BN, late_bh, &pb->v_full[vs]);
-                    tma_load_3d(dv + KV_HALF_BYTES, &tmV, 64, late_j * BN, late_bh, &pb->v_full[vs]);
+#pragma unroll
+                    for (int blk = 0; blk < NBLK; ++blk)
+                        tma_load_3d(dv + blk * KV_HALF_BYTES, &tmV, 64 * blk, late_j * BN, late_bh, &pb->v_full[vs]);
                 }
                 ++vt;
                 late_bh = -1;
@@ -550,8 +563,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (!wait_bar(&pb->k_empty[ks], ((kt / K_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
                 unsigned char *dk = sK + ks * KV_TILE_BYTES;
                 mbar_arrive_expect_tx(&pb->k_full[ks], KV_TILE_BYTES);
-                tma_load_3d(dk, &tmK, 0, j * BN, bh, &pb->k_full[ks]);
-                tma_load_3d(dk + KV_HALF_BYTES, &tmK, 64, j * BN, bh, &pb->k_full[ks]);
+#pragma unroll
+                for (int blk = 0; blk < NBLK; ++blk) tma_load_3d(dk + blk * KV_HALF_BYTES, &tmK, 64 * blk, j * BN, bh, &pb->k_full[ks]);
                 ++kt;
                 if (!load_v_late()) return false;
                 late_bh = bh;
@@ -627,8 +640,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         if (!ok) break;
                     }
                     mbar_arrive_expect_tx(q_full, TILE_BYTES);
-                    tma_load_3d(sQ_t, &tmQ, 0, t ? g.q0[1] : g.q0[0], bh, q_full);
-                    tma_load_3d(sQ_t + HALF_BYTES, &tmQ, 64, t ? g.q0[1] : g.q0[0], bh, q_full);
+#pragma unroll
+                    for (int blk = 0; blk < NBLK; ++blk) tma_load_3d(sQ_t + blk * HALF_BYTES, &tmQ, 64 * blk, t ? g.q0[1] : g.q0[0], bh, q_full);
                     ++nq;
                     continue;
                 }
@@ -796,7 +809,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         l2.y *= alpha;
                         uint32_t o[32];
 #pragma unroll 1
-                        for (int ch = 0; ch < 4; ++ch) {
+                        for (int ch = 0; ch < D / 32; ++ch) {
                             tmem_ld32(tO_t + lane_addr + ch * 32, o);
                             tmem_wait_ld(o);
 #pragma unroll
@@ -861,10 +874,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 unsigned char *gout = (unsigned char *)a.out + ((size_t)bh * a.S + row) * D * esz;
                 uint32_t o[32];
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < D / 32; ++ch) {
                     tmem_ld32(tO[t] + lane_addr + ch * 32, o);
                     tmem_wait_ld(o);
-                    if (ch == 3) { // O_t is in registers: the next item may overwrite it
+                    if (ch == D / 32 - 1) { // O_t is in registers: the next item may overwrite it
                         tc_fence_before();
                         mbar_arrive(&pb->o_empty[t]);
                     }
@@ -911,10 +924,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 // launchAttnQuantizedTransposeKernel (decoder_kernels.cu:1179-1300) restated: one block per token row
 // (b, s); absmax over all heads (floor -1e9f), scale = absmax / 127, codes cvt.rni.sat.s8(x*127/absmax),
 // [B,H,S,d] fp32 -> [B,S,H*d] int8.
+// One thread per head dimension (blockDim.x = head size: 64 or 128).
 __global__ void __launch_bounds__(128) flb_attn_quant_transpose_kernel(const float *__restrict__ attn, int8_t *__restrict__ q8,
                                                                       float *__restrict__ scale, int H, int S) {
     __shared__ float red[4];
-    const int s = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    const int s = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, D = (int)blockDim.x;
+    if (tid < 4) red[tid] = -1e9f;
+    __syncthreads();
     float amax = -1e9f;
     for (int h = 0; h < H; ++h) amax = fmaxf(amax, fabsf(attn[(((size_t)b * H + h) * S + s) * D + tid]));
 #pragma unroll
@@ -950,9 +966,9 @@ EncodeTiledFn encode_fn() {
     return reinterpret_cast<EncodeTiledFn>(fn);
 }
 
-// fp16 tensor [bh][rows_valid of rows_stride][128], box = 64 dims x box_rows rows, 128-byte swizzle;
+// fp16 tensor [bh][rows_valid of rows_stride][D], box = 64 dims x box_rows rows, 128-byte swizzle;
 // rows at or beyond rows_valid read as zeros.
-bool make_map(EncodeTiledFn enc, CUtensorMap *tm, const void *base, int BH, int rows_valid, int rows_stride, int box_rows) {
+bool make_map(EncodeTiledFn enc, CUtensorMap *tm, const void *base, int BH, int rows_valid, int rows_stride, int box_rows, int D) {
     const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows_valid, (cuuint64_t)BH};
     const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)rows_stride * D * 2};
     const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
@@ -962,9 +978,7 @@ bool make_map(EncodeTiledFn enc, CUtensorMap *tm, const void *base, int BH, int 
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-} // namespace
-
-int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
+template <int D> int launch_prefill_hd(const flb_attn_params *p, cudaStream_t stream) {
     if (p->freq_cis && (reinterpret_cast<uintptr_t>(p->freq_cis) & 15u)) return FLB_ERR_MISALIGNED;
     if (p->input_mode == FLB_IN_INT32 &&
         ((reinterpret_cast<uintptr_t>(p->q_w_scale) | reinterpret_cast<uintptr_t>(p->k_w_scale) |
@@ -1011,11 +1025,11 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     }
 
     CUtensorMap tmQ, tmK, tmV;
-    bool ok = make_map(enc, &tmQ, a.qh, B * H, S, S, BM);
+    bool ok = make_map(enc, &tmQ, a.qh, B * H, S, S, BM, D);
     if (a.cache_f16) {
-        ok = ok && make_map(enc, &tmK, p->k_cache, B * H, S, T, BN) && make_map(enc, &tmV, p->v_cache, B * H, S, T, BN);
+        ok = ok && make_map(enc, &tmK, p->k_cache, B * H, S, T, BN, D) && make_map(enc, &tmV, p->v_cache, B * H, S, T, BN, D);
     } else {
-        ok = ok && make_map(enc, &tmK, a.kh, B * H, S, S, BN) && make_map(enc, &tmV, a.vh, B * H, S, S, BN);
+        ok = ok && make_map(enc, &tmK, a.kh, B * H, S, S, BN, D) && make_map(enc, &tmV, a.vh, B * H, S, S, BN, D);
     }
     // the caller's v as a [batch][head][token][128] view of its [B,S,H,d] rows, for the V tiles taken from it directly
     CUtensorMap tmVin = tmV;
@@ -1033,18 +1047,19 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
 
     cudaLaunchConfig_t cfg = {};
     cfg.stream = stream;
-    const size_t pro_blocks = (size_t)B * H * ((S + 16 * kRowsPerThread - 1) / (16 * kRowsPerThread));
+    constexpr int pro_rows = (256 / (D / 8)) * kRowsPerThread; // token rows per block of the streaming pass
+    const size_t pro_blocks = (size_t)B * H * ((S + pro_rows - 1) / pro_rows);
     cfg.numAttrs = 0; // the prologue is launched the ordinary way (measured: starting it early costs 25 us)
     cfg.gridDim = dim3((unsigned)pro_blocks);
     cfg.blockDim = dim3(256);
     cfg.dynamicSmemBytes = 0;
     cudaError_t le;
     if (a.input_mode == 0)
-        le = cudaLaunchKernelEx(&cfg, flb_prefill_prologue_kernel<0>, a);
+        le = cudaLaunchKernelEx(&cfg, flb_prefill_prologue_kernel<0, D>, a);
     else if (a.input_mode == 1)
-        le = cudaLaunchKernelEx(&cfg, flb_prefill_prologue_kernel<1>, a);
+        le = cudaLaunchKernelEx(&cfg, flb_prefill_prologue_kernel<1, D>, a);
     else
-        le = cudaLaunchKernelEx(&cfg, flb_prefill_prologue_kernel<2>, a);
+        le = cudaLaunchKernelEx(&cfg, flb_prefill_prologue_kernel<2, D>, a);
     if (le != cudaSuccess) return FLB_ERR_LAUNCH;
 
     // The attention kernel is launched with programmatic stream serialisation: its CTAs set themselves up
@@ -1055,26 +1070,36 @@ int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
     pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     pdl[0].val.programmaticStreamSerializationAllowed = 1;
     const bool generic_mask = (a.mask_mode == FLB_MASK_GENERIC);
-    auto kern = generic_mask ? (a.out_f16 ? flb_prefill_attn_kernel<kExpOnFmaEvery, true, true> : flb_prefill_attn_kernel<kExpOnFmaEvery, true, false>)
-                             : (a.out_f16 ? flb_prefill_attn_kernel<kExpOnFmaEvery, false, true> : flb_prefill_attn_kernel<kExpOnFmaEvery, false, false>);
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefillSmem) != cudaSuccess) return FLB_ERR_LAUNCH;
+    auto kern = generic_mask ? (a.out_f16 ? flb_prefill_attn_kernel<kExpOnFmaEvery, true, true, D> : flb_prefill_attn_kernel<kExpOnFmaEvery, true, false, D>)
+                             : (a.out_f16 ? flb_prefill_attn_kernel<kExpOnFmaEvery, false, true, D> : flb_prefill_attn_kernel<kExpOnFmaEvery, false, false, D>);
+    constexpr size_t smem_bytes = prefill_smem(D);
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes) != cudaSuccess) return FLB_ERR_LAUNCH;
     const long long num_items = (long long)B * H * ((S + 2 * BM - 1) / (2 * BM));
     cfg.attrs = pdl;
     cfg.numAttrs = 1;
     cfg.gridDim = dim3((unsigned)(num_items < sms ? num_items : sms));
     cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = kPrefillSmem;
+    cfg.dynamicSmemBytes = smem_bytes;
     if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, tmVin, a, (int)num_items) != cudaSuccess) return FLB_ERR_LAUNCH;
     if (p->out_q8) {
-        flb_attn_quant_transpose_kernel<<<dim3((unsigned)S, (unsigned)B), 128, 0, stream>>>((const float *)p->out, p->out_q8,
-                                                                                           p->out_q8_scale, H, S);
+        flb_attn_quant_transpose_kernel<<<dim3((unsigned)S, (unsigned)B), D, 0, stream>>>((const float *)p->out, p->out_q8,
+                                                                                         p->out_q8_scale, H, S);
         if (cudaGetLastError() != cudaSuccess) return FLB_ERR_LAUNCH;
     }
     return FLB_OK;
 }
 
-int launch_quantize(const float *attn, int8_t *q8, float *scale, int B, int H, int S, cudaStream_t stream) {
-    flb_attn_quant_transpose_kernel<<<dim3((unsigned)S, (unsigned)B), 128, 0, stream>>>(attn, q8, scale, H, S);
+} // namespace
+
+int launch_prefill(const flb_attn_params *p, cudaStream_t stream) {
+    if (p->size_per_head == 128) return launch_prefill_hd<128>(p, stream);
+    if (p->size_per_head == 64) return launch_prefill_hd<64>(p, stream);
+    return FLB_ERR_UNSUPPORTED;
+}
+
+int launch_quantize(const float *attn, int8_t *q8, float *scale, int B, int H, int S, int d, cudaStream_t stream) {
+    if (d != 64 && d != 128) return FLB_ERR_UNSUPPORTED;
+    flb_attn_quant_transpose_kernel<<<dim3((unsigned)S, (unsigned)B), (unsigned)d, 0, stream>>>(attn, q8, scale, H, S);
     return cudaGetLastError() == cudaSuccess ? FLB_OK : FLB_ERR_LAUNCH;
 }
 

@@ -78,7 +78,7 @@ typedef struct flb_attn_params {
     /* dimensions (names follow OpenDecoder's constructor, open_decoder.h:65) */
     int batch_size;    /* B                                                              */
     int head_num;      /* H                                                              */
-    int size_per_head; /* d: 128; decode calls (seq_len == 1) also take 64 and 256       */
+    int size_per_head; /* d: 64 or 128; decode calls (seq_len == 1) also take 256          */
     int seq_len;       /* S, tokens of this call per sequence: 1 = decode, >1 = prefill  */
     int start_pos;     /* rows already in the cache, same for every sequence
                           (OpenDecoder::forward's start_pos)                             */
@@ -307,7 +307,7 @@ int flb_attn_static_scratch_status(unsigned *status_out, void *cuda_stream);
  * fasterLlama/cuda/decoder_kernels.cu:1179-1300, called at open_decoder.cu:245): attn fp32 [B,H,S,d] ->
  * q8 int8 [B,S,H*d] + scale fp32 [B*S] (absmax over all heads of a token row / 127, floor -1e9f).  The
  * fused forms (flb_attn_params::out_q8, flb_peer_exchange::out_q8) do the same arithmetic; this entry is
- * for callers that assemble the [B,H,S,d] tensor themselves, e.g. after an all-gather.  d must be 128. */
+ * for callers that assemble the [B,H,S,d] tensor themselves, e.g. after an all-gather.  d is 64 or 128. */
 int flb_attn_quantize(const float *attn, int8_t *q8, float *scale, int batch_size, int head_num, int seq_len,
                       int size_per_head, void *cuda_stream);
 

@@ -32,13 +32,15 @@ CASES = {
 
 
 # Decode at the other head sizes the call accepts (the reference's kernels take them too: size_per_head <= 128 on
-# its warp kernels, 256 on its block kernels, decoder_kernels.cu:563-589).  Their vectors live in a fixture of their
-# own, ref_golden_head_sizes.npz, made by `make_ref_golden.py <out> head_sizes`.
+# its warp kernels, 256 on its block kernels, decoder_kernels.cu:563-589), and prefill at head size 64.  Their vectors
+# live in a fixture of their own, ref_golden_head_sizes.npz, made by `make_ref_golden.py <out> head_sizes`.
 HEAD_SIZE_CASES = {
     "decode_d64_L200_inclusive": dict(B=2, H=8, S=1, T=256, start_pos=199, mask="inclusive", rope_row=199, d=64),
     "decode_d64_L700_strict": dict(B=1, H=8, S=1, T=768, start_pos=699, mask="strict", rope_row=0, d=64),
     "decode_d256_L150_none": dict(B=2, H=8, S=1, T=192, start_pos=149, mask="none", rope_row=149, d=256),
     "decode_d256_L600_inclusive": dict(B=1, H=8, S=1, T=640, start_pos=599, mask="inclusive", rope_row=599, d=256),
+    "prefill_d64_S200_inclusive": dict(B=1, H=8, S=200, T=256, start_pos=0, mask="inclusive", rope_row=0, d=64),
+    "prefill_d64_S330_strict": dict(B=1, H=8, S=330, T=384, start_pos=0, mask="strict", rope_row=0, d=64),
 }
 
 

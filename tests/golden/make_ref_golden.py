@@ -3,7 +3,7 @@ cuBLAS calls (oracle/_ref/libflb_ref.so, built by oracle/build_ref.sh from the r
 on the deterministic inputs of golden_cases.py.  Needs a GPU:
 
     python tests/golden/make_ref_golden.py <output.npz>                  (ref_golden.npz: the head-size-128 cases)
-    python tests/golden/make_ref_golden.py <output.npz> head_sizes       (ref_golden_head_sizes.npz: decode at 64 and 256)
+    python tests/golden/make_ref_golden.py <output.npz> head_sizes       (ref_golden_head_sizes.npz: decode at 64 and 256, prefill at 64)
 
 Stored per case (prefill cases: for the heads in golden_cases.PREFILL_HEADS_KEPT only, to keep
 the fixture small): the attention output, the cache rows the call appended, the RoPE table rows it

@@ -147,5 +147,5 @@ def test_exchange_and_quantize_argument_checks_need_no_gpu():
     x.out_q8 = None
     assert lib.flb_attn_peer_exchange(C.byref(x), None) == _lib.FLB_ERR_NULL_POINTER  # rank 1's flag words missing
     assert lib.flb_attn_quantize(None, None, None, 1, 1, 1, 128, None) == _lib.FLB_ERR_NULL_POINTER
-    assert lib.flb_attn_quantize(4096, 4096, 4096, 1, 1, 1, 64, None) == _lib.FLB_ERR_UNSUPPORTED
+    assert lib.flb_attn_quantize(4096, 4096, 4096, 1, 1, 1, 96, None) == _lib.FLB_ERR_UNSUPPORTED
     assert lib.flb_attn_quantize(4096, 4096, 4096, 0, 1, 1, 128, None) == _lib.FLB_ERR_BAD_SHAPE
