@@ -121,8 +121,8 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *tm, const void *
                  : "memory");
 }
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// every bulk group of this thread has finished READING its shared-memory source (the source may be overwritten)
-__device__ __forceinline__ void bulk_wait_group_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all but the N newest bulk groups of this thread have finished READING their shared-memory source (it may be overwritten)
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 // every bulk group of this thread has completed
 __device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *tm) {
