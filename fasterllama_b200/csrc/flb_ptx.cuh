@@ -113,8 +113,20 @@ __device__ __forceinline__ void tma_load_4d(void *dst_smem, const CUtensorMap *t
                  "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
                  : "memory");
 }
+// The same for a rank-5 map.
+__device__ __forceinline__ void tma_load_5d(void *dst_smem, const CUtensorMap *tm, int c0, int c1, int c2, int c3, int c4, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar))
+                 : "memory");
+}
 // Tiled TMA store of one box from this CTA's shared memory (part of the thread's current bulk group).  Coordinates must
 // not be negative; elements outside the tensor's extent are not written.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *tm, const void *src_smem, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tm), "r"(smem_u32(src_smem)),
+                 "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap *tm, const void *src_smem, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tm), "r"(smem_u32(src_smem)),
                  "r"(c0), "r"(c1), "r"(c2)

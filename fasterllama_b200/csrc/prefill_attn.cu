@@ -19,12 +19,14 @@
 //    keys.  TMEM (512 columns): per query tile two score buffers of 64 columns (fp32 scores; P overwrites them as
 //    fp16 pairs) and 128 columns of fp32 accumulator O.  Warp roles:
 //      warp 0      work scheduler + K/V loader: TMA boxes (128-byte swizzle) into a ring of K tiles and a ring of V
-//                  tiles (64 keys each).  A K tile goes back to the loader when both query tiles' S over it have
+//                  tiles (64 keys each); the tensor maps carry the 64-dim block of a row as a dimension of its own,
+//                  so one instruction brings a whole tile (a single issuing thread pays 100-250 cycles per TMA
+//                  instruction).  A K tile goes back to the loader when both query tiles' S over it have
 //                  landed, a V tile when both query tiles' P.V over it have retired: K is needed two tiles earlier
 //                  than V and is free two tiles earlier, so two rings do in 96-128 KB what one ring needed 160 KB for.
-//                  With fp16 inputs and an fp16 cache the V tiles come straight from the caller's v (a rank-4 tensor
-//                  map over its [B,S,H,d] rows) and the loader stores them into the cache from the ring (TMA store)
-//                  when their stage comes up for reuse: the streaming pass in front then moves q and k only
+//                  With fp16 inputs and an fp16 cache the V tiles come straight from the caller's v (a rank-5 tensor
+//                  map over its [B,S,H,d] rows) and the loader stores them into the cache from the ring (TMA store,
+//                  two loader steps after the load, never waited for): the streaming pass in front then moves q and k only
 //      warps 1, 3  issue S = Q_t.K_j^T for query tile 0 / 1 (SS form: both operands in shared memory, 128 x 64 x 16
 //                  per instruction) and load that tile's query rows.  S runs TWO key tiles ahead of P.V: while
 //                  the softmax threads work on S_j, S_{j+1} is already in TMEM, so they never wait for the pipe;
@@ -399,7 +401,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                             const int num_items) {
     // The 128-byte swizzle pattern is a function of address bits [4,10): tiles must start on 1 KB.
     constexpr int D = HD;
-    constexpr int NBLK = D / 64;                      // 64-dim blocks per tile
     constexpr int TILE_BYTES = BM * D * 2;
     constexpr int KV_TILE_BYTES = BN * D * 2;
     static_assert(D == 64 || D == 128, "O_t takes D TMEM columns per query tile beside the 256 columns of scores");
@@ -526,8 +527,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (!wait_bar(&pb->v_full[ss], (st / V_STAGES) & 1u, pb, a.status)) return false;
                 const int sj = pb->v_store_j[ss];
                 unsigned char *dv = sV + ss * KV_TILE_BYTES;
-#pragma unroll
-                for (int blk = 0; blk < NBLK; ++blk) tma_store_3d(&tmV, dv + blk * KV_HALF_BYTES, 64 * blk, sj * BN, sbh);
+                tma_store_4d(&tmV, dv, 0, sj * BN, 0, sbh);
                 pb->v_store_bh[ss] = -1;
                 return true;
             };
@@ -554,14 +554,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     }
                     const int b = late_bh / a.H, h = late_bh - b * a.H;
                     mbar_arrive_expect_tx(&pb->v_full[vs], KV_TILE_BYTES);
-#pragma unroll
-                    for (int blk = 0; blk < NBLK; ++blk)
-                        tma_load_4d(dv + blk * KV_HALF_BYTES, &tmVin, 64 * blk, late_j * BN, h, b, &pb->v_full[vs]);
+                    tma_load_5d(dv, &tmVin, 0, late_j * BN, 0, h, b, &pb->v_full[vs]);
                 } else {
                     mbar_arrive_expect_tx(&pb->v_full[vs], KV_TILE_BYTES);
-#pragma unroll
-                    for (int blk = 0; blk < NBLK; ++blk)
-                        tma_load_3d(dv + blk * KV_HALF_BYTES, &tmV, 64 * blk, late_j * BN, late_bh, &pb->v_full[vs]);
+                    tma_load_4d(dv, &tmV, 0, late_j * BN, 0, late_bh, &pb->v_full[vs]);
                 }
                 ++vt;
                 late_bh = -1;
@@ -572,8 +568,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (!wait_bar(&pb->k_empty[ks], ((kt / K_STAGES) & 1u) ^ 1u, pb, a.status)) return false;
                 unsigned char *dk = sK + ks * KV_TILE_BYTES;
                 mbar_arrive_expect_tx(&pb->k_full[ks], KV_TILE_BYTES);
-#pragma unroll
-                for (int blk = 0; blk < NBLK; ++blk) tma_load_3d(dk + blk * KV_HALF_BYTES, &tmK, 64 * blk, j * BN, bh, &pb->k_full[ks]);
+                tma_load_4d(dk, &tmK, 0, j * BN, 0, bh, &pb->k_full[ks]);
                 ++kt;
                 if (!load_v_late()) return false;
                 late_bh = bh;
@@ -645,8 +640,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         if (!ok) break;
                     }
                     mbar_arrive_expect_tx(q_full, TILE_BYTES);
-#pragma unroll
-                    for (int blk = 0; blk < NBLK; ++blk) tma_load_3d(sQ_t + blk * HALF_BYTES, &tmQ, 64 * blk, t ? g.q0[1] : g.q0[0], bh, q_full);
+                    tma_load_4d(sQ_t, &tmQ, 0, t ? g.q0[1] : g.q0[0], 0, bh, q_full);
                     ++nq;
                     continue;
                 }
@@ -971,14 +965,15 @@ EncodeTiledFn encode_fn() {
     return reinterpret_cast<EncodeTiledFn>(fn);
 }
 
-// fp16 tensor [bh][rows_valid of rows_stride][D], box = 64 dims x box_rows rows, 128-byte swizzle;
-// rows at or beyond rows_valid read as zeros.
+// fp16 tensor [bh][rows_valid of rows_stride][D] seen as [bh][D/64 blocks][rows][64]: one box = box_rows rows of every
+// 64-dim block, which lands in shared memory block after block, each [box_rows x 64] in the 128-byte-swizzled operand
+// layout — a whole tile with one instruction.  Rows at or beyond rows_valid read as zeros.
 bool make_map(EncodeTiledFn enc, CUtensorMap *tm, const void *base, int BH, int rows_valid, int rows_stride, int box_rows, int D) {
-    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows_valid, (cuuint64_t)BH};
-    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)rows_stride * D * 2};
-    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    return enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+    const cuuint64_t dims[4] = {64, (cuuint64_t)rows_valid, (cuuint64_t)(D / 64), (cuuint64_t)BH};
+    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, 128, (cuuint64_t)rows_stride * D * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, (cuuint32_t)(D / 64), 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -1039,11 +1034,11 @@ template <int D> int launch_prefill_hd(const flb_attn_params *p, cudaStream_t st
     // the caller's v as a [batch][head][token][128] view of its [B,S,H,d] rows, for the V tiles taken from it directly
     CUtensorMap tmVin = tmV;
     if (ok && a.v_direct) {
-        const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
-        const cuuint64_t strides[3] = {(cuuint64_t)a.row_stride * 2, (cuuint64_t)D * 2, (cuuint64_t)S * a.row_stride * 2};
-        const cuuint32_t box[4] = {64, (cuuint32_t)BN, 1, 1};
-        const cuuint32_t estr[4] = {1, 1, 1, 1};
-        ok = enc(&tmVin, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(a.v), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        const cuuint64_t dims[5] = {64, (cuuint64_t)S, (cuuint64_t)(D / 64), (cuuint64_t)H, (cuuint64_t)B};
+        const cuuint64_t strides[4] = {(cuuint64_t)a.row_stride * 2, 128, (cuuint64_t)D * 2, (cuuint64_t)S * a.row_stride * 2};
+        const cuuint32_t box[5] = {64, (cuuint32_t)BN, (cuuint32_t)(D / 64), 1, 1};
+        const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        ok = enc(&tmVin, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void *>(a.v), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
     }
     if (!ok) return FLB_ERR_LAUNCH;
