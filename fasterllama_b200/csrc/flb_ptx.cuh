@@ -98,15 +98,8 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 
 namespace flb {
 
-// Tiled TMA load of one box of a rank-3 tensor map into this CTA's own shared memory.
+// Tiled TMA load of one box of a rank-4 tensor map into this CTA's own shared memory.
 // c0 is the innermost coordinate: c0 * element size must be a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_3d(void *dst_smem, const CUtensorMap *tm, int c0, int c1, int c2, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
-                     smem_u32(dst_smem)),
-                 "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
-                 : "memory");
-}
-// The same for a rank-4 map.
 __device__ __forceinline__ void tma_load_4d(void *dst_smem, const CUtensorMap *tm, int c0, int c1, int c2, int c3, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
                      smem_u32(dst_smem)),
@@ -125,11 +118,6 @@ __device__ __forceinline__ void tma_load_5d(void *dst_smem, const CUtensorMap *t
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap *tm, const void *src_smem, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tm), "r"(smem_u32(src_smem)),
                  "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-                 : "memory");
-}
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap *tm, const void *src_smem, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tm), "r"(smem_u32(src_smem)),
-                 "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
 }
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
