@@ -17,7 +17,7 @@
 //    warps per SM.  A work item is 256 query rows of one (b,h) (two 128-row query tiles); items are handed out through
 //    an atomic counter, heavy (late) query blocks first, in groups of heads whose K/V stay in L2.  Key tiles hold 64
 //    keys.  TMEM (512 columns): per query tile two score buffers of 64 columns (fp32 scores; P overwrites them as
-//    fp16 pairs) and 128 columns of fp32 accumulator O.  Warp roles:
+//    fp16 pairs) and one column of fp32 accumulator O per head dimension (128 or 64).  Warp roles:
 //      warp 0      work scheduler + K/V loader: TMA boxes (128-byte swizzle) into a ring of K tiles and a ring of V
 //                  tiles (64 keys each); the tensor maps carry the 64-dim block of a row as a dimension of its own,
 //                  so one instruction brings a whole tile (a single issuing thread pays 100-250 cycles per TMA
